@@ -1,0 +1,126 @@
+/*
+ * rq_b200.h -- C ABI of librq_b200.so: the RotorQuant KV-cache hot path for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Every entry point replaces one Python/Triton launcher of the reference
+ * project (tpurtell/rotorquant-vllm, paths relative to its root).  All
+ * pointers are raw device pointers owned by the caller unless stated
+ * otherwise; the library allocates nothing, never synchronises the host and
+ * only enqueues work on `stream` (a cudaStream_t passed as void*).  Functions
+ * return RQ_OK (0) or a negative rq_status; rq_last_error() gives the message
+ * of the last failure on the calling thread.
+ *
+ * Cache layout (src/rotorquant_vllm/vllm/rq_backend.py:155-188, :484-490):
+ * uint8 (num_blocks, block_size, total_bytes), one slot per token:
+ *
+ *   [0, H*64)        K indices, 64 B per head: byte j = idx[2j] << 4 | idx[2j+1]
+ *   [H*64, H*68)     K norms, fp32 little endian
+ *   [H*68, H*132)    V indices
+ *   [H*132, H*136)   V norms
+ *   [H*136, H*256)   zero padding           total_bytes = H * 256  (head_dim 128)
+ *
+ * The rotation is passed the way the reference passes it: the dense row-major
+ * (head_dim x head_dim) fp32 matrix R.  It must be block diagonal with 4x4
+ * blocks (IsoQuant) or 2x2 blocks (PlanarQuant); only the 4x4 diagonal blocks
+ * are read.
+ */
+#ifndef RQ_B200_H
+#define RQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    RQ_OK = 0,
+    RQ_ERR_INVALID_ARG = -1,  /* null pointer, negative size, inconsistent shapes      */
+    RQ_ERR_UNSUPPORTED = -2,  /* head_dim != 128, bits not 3/4, group size > 16, ...    */
+    RQ_ERR_ALIGNMENT = -3,    /* a pointer or stride breaks the stated alignment        */
+    RQ_ERR_WORKSPACE = -4,    /* workspace missing or too small                         */
+    RQ_ERR_CUDA = -5          /* a CUDA runtime call failed; message has the CUDA text  */
+} rq_status;
+
+typedef enum { RQ_DTYPE_F32 = 0, RQ_DTYPE_F16 = 1, RQ_DTYPE_BF16 = 2 } rq_dtype;
+
+/* Library identification, e.g. "rq_b200 0.1 (sm_100a)". */
+const char* rq_version(void);
+
+/* Message of the most recent failure on this thread ("" if none). */
+const char* rq_last_error(void);
+
+/*
+ * Compress new K and V tokens and write whole slots into the paged cache.
+ * Replaces RQAttentionImpl._compress_and_store (vllm/rq_backend.py:585-657),
+ * i.e. two iso_compress / planar_compress launches
+ * (triton/isoquant_compress.py:104-158, triton/planarquant_compress.py:100-154)
+ * plus the row assembly and scatter.  Bytes and norms equal the reference's
+ * PyTorch path (triton/isoquant_compress.py:161-190) bit for bit.
+ *
+ *   key, value     (num_tokens, H, 128) in `in_dtype`, last dim contiguous; strides in elements;
+ *                  rows must start on 16-byte boundaries
+ *   slot_mapping   int64[num_tokens]: flat slot = block * block_size + offset; negative = skip
+ *   boundaries     ascending fp32 Lloyd-Max boundaries, 7 (3-bit) or 15 (4-bit) entries
+ *   write_padding  non-zero: zero bytes [H*136, H*256) of each written slot (reference behaviour)
+ */
+int rq_compress_store(const void* key, const void* value, int in_dtype, int64_t num_tokens,
+                      int num_kv_heads, int head_dim, int64_t k_token_stride,
+                      int64_t k_head_stride, int64_t v_token_stride, int64_t v_head_stride,
+                      uint8_t* kv_cache, int64_t num_slots, int total_bytes,
+                      const int64_t* slot_mapping, const float* rotation,
+                      const float* k_boundaries, int n_k_boundaries, const float* v_boundaries,
+                      int n_v_boundaries, int write_padding, void* stream);
+
+/*
+ * Compress rows without the cache: x (num_rows, 128) -> packed (num_rows, 64) uint8 and
+ * norms (num_rows) fp32.  Replaces iso_compress / planar_compress
+ * (triton/isoquant_compress.py:104-158, triton/planarquant_compress.py:100-154).
+ */
+int rq_compress(const void* x, int in_dtype, int64_t num_rows, int head_dim, int64_t row_stride,
+                const float* rotation, const float* boundaries, int n_boundaries,
+                uint8_t* packed_out, float* norms_out, void* stream);
+
+/*
+ * Decompress rows: packed (num_rows, 64) + norms (num_rows) -> out (num_rows, 128) in out_dtype,
+ * centroid[idx] * norm rounded once; stays in rotated space.  Replaces iso_decompress /
+ * planar_decompress (triton/isoquant_decompress.py:63-100, triton/planarquant_decompress.py:63-101).
+ */
+int rq_decompress(const uint8_t* packed, const float* norms, int64_t num_rows, int head_dim,
+                  const float* centroids, int n_centroids, void* out, int out_dtype,
+                  void* stream);
+
+/*
+ * Scratch bytes rq_decode needs for `num_splits` context splits (0 = let the library choose
+ * from max_seq_len; the same choice rq_decode makes).
+ */
+size_t rq_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                 int max_seq_len, int num_splits);
+
+/*
+ * Fused paged decode attention, one query token per sequence.  Replaces
+ * fused_paged_rq_decode (triton/fused_paged_rq_decode.py:214-312) including the two dense
+ * rotations around the kernel (:271, :308): q is rotated by R^T, attention runs in rotated
+ * space over centroid[idx] * norm, the result is rotated back by R.
+ *
+ *   q, out        (num_seqs, H_Q, 128) in `dtype` (f16 or bf16); strides in elements
+ *   block_table   int32 (num_seqs, >= ceil(seq_len / block_size)), row stride in elements
+ *   seq_lens      int32[num_seqs]; 0 gives a zero output row
+ *   max_seq_len   upper bound of seq_lens (host value; sizes the grid, never read from device)
+ *   workspace     >= rq_decode_workspace_bytes(...) bytes, 16-byte aligned
+ *   num_splits    context splits per sequence, 0 = automatic
+ */
+int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq, int64_t q_stride_head,
+              int64_t o_stride_seq, int64_t o_stride_head, int num_seqs, int num_q_heads,
+              int num_kv_heads, int head_dim, const uint8_t* kv_cache, int64_t num_blocks,
+              int block_size, int total_bytes, const int32_t* block_table,
+              int64_t block_table_stride, const int32_t* seq_lens, const float* centroids_k,
+              int n_centroids_k, const float* centroids_v, int n_centroids_v,
+              const float* rotation, float sm_scale, int max_seq_len, void* workspace,
+              size_t workspace_bytes, int num_splits, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RQ_B200_H */

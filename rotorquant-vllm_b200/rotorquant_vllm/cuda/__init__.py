@@ -1,0 +1,18 @@
+"""Kernel launchers of the B200 build: the host-side mirror of the reference's
+``rotorquant_vllm.triton`` package, calling librq_b200.so through its C ABI."""
+
+from .compress import compress_and_store, iso_compress, planar_compress
+from .decode import decode_workspace_bytes, fused_paged_rq_decode
+from .decompress import iso_decompress, planar_decompress
+from .rotation import validate_rotation
+
+__all__ = [
+    "iso_compress",
+    "planar_compress",
+    "iso_decompress",
+    "planar_decompress",
+    "compress_and_store",
+    "fused_paged_rq_decode",
+    "decode_workspace_bytes",
+    "validate_rotation",
+]
