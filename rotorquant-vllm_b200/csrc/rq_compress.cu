@@ -48,7 +48,7 @@ struct CompressParams {
 __device__ __forceinline__ void compress_row(const float* __restrict__ x,
                                              const float* __restrict__ rot,   // [32][4][4]
                                              const float* __restrict__ bnd, int nb,
-                                             uint4* packed, float& norm_out) {
+                                             uint32_t* packed, bool vec16, float& norm_out) {
     float s[8];
 #pragma unroll
     for (int l = 0; l < 8; ++l) s[l] = 0.0f;
@@ -102,7 +102,13 @@ __device__ __forceinline__ void compress_row(const float* __restrict__ x,
             }
             words[w] = word;
         }
-        packed[i] = make_uint4(words[0], words[1], words[2], words[3]);
+        // The V index region of a slot starts at H*68 bytes: 16-byte aligned only when H % 4 == 0.
+        if (vec16) {
+            reinterpret_cast<uint4*>(packed)[i] = make_uint4(words[0], words[1], words[2], words[3]);
+        } else {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) packed[4 * i + w] = words[w];
+        }
     }
 }
 
@@ -197,9 +203,9 @@ compress_store_kernel(const CompressParams p) {
             const int tl = rem / H, h = rem % H;
             float norm;
             uint8_t* slot = sm.stage + tl * lay.total;
-            uint4* dst = reinterpret_cast<uint4*>(slot + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim);
+            uint32_t* dst = reinterpret_cast<uint32_t*>(slot + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim);
             compress_row(sm.rows + threadIdx.x * kRowPitch, sm.rot, sm.bnd + 16 * kv,
-                         p.n_bounds[kv], dst, norm);
+                         p.n_bounds[kv], dst, (lay.v_idx % 16) == 0, norm);
             *reinterpret_cast<float*>(slot + (kv ? lay.v_norm : lay.k_norm) + 4 * h) = norm;
         }
     }
@@ -232,8 +238,8 @@ compress_rows_kernel(const CompressParams p) {
     __syncthreads();
     if (threadIdx.x < rows_used) {
         float norm;
-        uint4* dst = reinterpret_cast<uint4*>(p.packed_out + (r0 + threadIdx.x) * kHalfDim);
-        compress_row(sm.rows + threadIdx.x * kRowPitch, sm.rot, sm.bnd, p.n_bounds[0], dst, norm);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(p.packed_out + (r0 + threadIdx.x) * kHalfDim);
+        compress_row(sm.rows + threadIdx.x * kRowPitch, sm.rot, sm.bnd, p.n_bounds[0], dst, true, norm);
         p.norms_out[r0 + threadIdx.x] = norm;
     }
 }

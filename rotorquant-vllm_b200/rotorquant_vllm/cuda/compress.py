@@ -13,23 +13,26 @@ import torch
 from .. import _lib
 from .rotation import validate_rotation
 
-_DENSE_R: dict[tuple, torch.Tensor] = {}
+# (id(even), id(odd), versions) -> (even, odd, R).  The inputs are kept alive by the entry, so
+# neither their ids nor their storage can be reused by another tensor while it is cached.
+_DENSE_R: dict[tuple, tuple] = {}
 
 
 def _dense_rotation(rot_T_even: torch.Tensor, rot_T_odd: torch.Tensor) -> torch.Tensor:
     """``R`` from the even / odd column halves of ``R^T`` the reference API passes around."""
-    key = (rot_T_even.data_ptr(), rot_T_odd.data_ptr(), rot_T_even._version, rot_T_odd._version)
-    r = _DENSE_R.get(key)
-    if r is None:
-        d = rot_T_even.shape[0]
-        rot_t = torch.empty(d, d, dtype=torch.float32, device=rot_T_even.device)
-        rot_t[:, 0::2] = rot_T_even
-        rot_t[:, 1::2] = rot_T_odd
-        r = rot_t.T.contiguous()
-        validate_rotation(r)
-        if len(_DENSE_R) > 64:
-            _DENSE_R.clear()
-        _DENSE_R[key] = r
+    key = (id(rot_T_even), id(rot_T_odd), rot_T_even._version, rot_T_odd._version)
+    hit = _DENSE_R.get(key)
+    if hit is not None:
+        return hit[2]
+    d = rot_T_even.shape[0]
+    rot_t = torch.empty(d, d, dtype=torch.float32, device=rot_T_even.device)
+    rot_t[:, 0::2] = rot_T_even
+    rot_t[:, 1::2] = rot_T_odd
+    r = rot_t.T.contiguous()
+    validate_rotation(r)
+    if len(_DENSE_R) >= 8:
+        _DENSE_R.pop(next(iter(_DENSE_R)))
+    _DENSE_R[key] = (rot_T_even, rot_T_odd, r)
     return r
 
 
