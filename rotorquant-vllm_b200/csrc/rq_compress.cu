@@ -1,32 +1,36 @@
 // Compress-on-cache-write for RotorQuant (IsoQuant / PlanarQuant), sm_100a.
 //
-// One pass over the new tokens: L2 norm, normalise, block-diagonal rotation,
-// boundary bucketize, nibble pack, and the scatter of whole cache slots.
-// Replaces the reference's per-row Triton kernel (triton/isoquant_compress.py:16-96) plus the
-// row assembly and scatter in RQAttentionImpl._compress_and_store (vllm/rq_backend.py:585-657).
+// One pass over the new tokens: L2 norm, normalise, block-diagonal rotation, boundary bucketize,
+// nibble pack, and the scatter into the paged cache.  Replaces the reference's per-row Triton
+// kernel (triton/isoquant_compress.py:16-96) plus the row assembly and scatter in
+// RQAttentionImpl._compress_and_store (vllm/rq_backend.py:585-657).
 //
 // Bit-exactness.  The bytes must equal the reference's PyTorch path
-// (triton/isoquant_compress.py:161-190), so every row is evaluated by ONE thread with the
-// IEEE-754 operations of that path in their order:
+// (triton/isoquant_compress.py:161-190), so each value is produced by the IEEE-754 operations of
+// that path in their order:
 //   norm   : eight running sums s_l += x[8c+l]^2 (multiply and add rounded separately,
 //            c ascending), combined left to right, correctly rounded sqrt
 //   divide : x / (norm + 1e-10f), IEEE division
 //   rotate : out_j = fma(x3,R[j][3], fma(x2,R[j][2], fma(x1,R[j][1], x0*R[j][0]))) per 4x4 block
 //   bucket : number of boundaries strictly below the value
-// Rows are staged through shared memory so that global loads and the slot stores are
-// coalesced 16-byte accesses although the arithmetic is thread-per-row.
+//
+// Mapping.  Sixteen threads share a row of 128 values: thread j owns elements 8j..8j+7 (one
+// 16-byte load for 2-byte inputs), i.e. two rotation blocks and one 32-bit word of packed
+// output, so loads and stores of a half-warp are contiguous.  Only the norm needs the whole
+// row: the squares go through shared memory, threads 0..7 of the row form the eight running
+// sums in the prescribed order, and the left-to-right combination is done with shuffles.
 #include "rq_common.cuh"
 
 namespace rq {
 
-constexpr int kCompressThreads = 128;       // rows per CTA pass
-constexpr int kRowPitch = kHeadDim + 4;     // floats; +4 keeps float4 reads conflict-free
+constexpr int kCompressThreads = 256;                 // 16 rows per CTA
+constexpr int kRowsPerCta = kCompressThreads / 16;
 
 struct CompressParams {
     const void* src[2];          // key, value (or x, unused)
     int64_t token_stride[2];     // elements
     int64_t head_stride[2];      // elements
-    int64_t num_tokens;
+    int64_t num_tokens;          // tokens (store variant) or rows (rows variant)
     int H;
     // cache destination (store variant)
     uint8_t* cache;
@@ -34,7 +38,6 @@ struct CompressParams {
     int total_bytes;
     const int64_t* slot_mapping;
     int write_padding;
-    int tokens_per_cta;
     // plain-row destination (rows variant)
     uint8_t* packed_out;
     float* norms_out;
@@ -44,204 +47,153 @@ struct CompressParams {
     int n_bounds[2];
 };
 
-// Compress one row held in shared memory as 128 floats.
-__device__ __forceinline__ void compress_row(const float* __restrict__ x,
-                                             const float* __restrict__ rot,   // [32][4][4]
-                                             const float* __restrict__ bnd, int nb,
-                                             uint32_t* packed, bool vec16, float& norm_out) {
-    float s[8];
-#pragma unroll
-    for (int l = 0; l < 8; ++l) s[l] = 0.0f;
-#pragma unroll 4
-    for (int c = 0; c < kHeadDim / 8; ++c) {
-        const float4 a = *reinterpret_cast<const float4*>(x + 8 * c);
-        const float4 b = *reinterpret_cast<const float4*>(x + 8 * c + 4);
-        s[0] = __fadd_rn(s[0], __fmul_rn(a.x, a.x));
-        s[1] = __fadd_rn(s[1], __fmul_rn(a.y, a.y));
-        s[2] = __fadd_rn(s[2], __fmul_rn(a.z, a.z));
-        s[3] = __fadd_rn(s[3], __fmul_rn(a.w, a.w));
-        s[4] = __fadd_rn(s[4], __fmul_rn(b.x, b.x));
-        s[5] = __fadd_rn(s[5], __fmul_rn(b.y, b.y));
-        s[6] = __fadd_rn(s[6], __fmul_rn(b.z, b.z));
-        s[7] = __fadd_rn(s[7], __fmul_rn(b.w, b.w));
-    }
-    float tot = s[0];
-#pragma unroll
-    for (int l = 1; l < 8; ++l) tot = __fadd_rn(tot, s[l]);
-    const float norm = __fsqrt_rn(tot);
-    norm_out = norm;
-    const float denom = __fadd_rn(norm, 1e-10f);
-
-#pragma unroll 1
-    for (int i = 0; i < 4; ++i) {               // 16 output bytes = 8 blocks of four values
-        uint32_t words[4];
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {           // one 32-bit word = two blocks = 8 indices
-            uint32_t word = 0;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int g = 8 * i + 2 * w + half;
-                const float4 xv = *reinterpret_cast<const float4*>(x + 4 * g);
-                const float x0 = __fdiv_rn(xv.x, denom), x1 = __fdiv_rn(xv.y, denom);
-                const float x2 = __fdiv_rn(xv.z, denom), x3 = __fdiv_rn(xv.w, denom);
-                uint32_t idx[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float4 r = *reinterpret_cast<const float4*>(rot + g * 16 + j * 4);
-                    float acc = __fmul_rn(x0, r.x);
-                    acc = __fmaf_rn(x1, r.y, acc);
-                    acc = __fmaf_rn(x2, r.z, acc);
-                    acc = __fmaf_rn(x3, r.w, acc);
-                    uint32_t n = 0;
-                    for (int b = 0; b < nb; ++b) n += (bnd[b] < acc) ? 1u : 0u;
-                    idx[j] = n > 15u ? 15u : n;
-                }
-                const uint32_t b0 = (idx[0] << 4) | idx[1];
-                const uint32_t b1 = (idx[2] << 4) | idx[3];
-                word |= (b0 | (b1 << 8)) << (16 * half);
-            }
-            words[w] = word;
-        }
-        // The V index region of a slot starts at H*68 bytes: 16-byte aligned only when H % 4 == 0.
-        if (vec16) {
-            reinterpret_cast<uint4*>(packed)[i] = make_uint4(words[0], words[1], words[2], words[3]);
-        } else {
-#pragma unroll
-            for (int w = 0; w < 4; ++w) packed[4 * i + w] = words[w];
-        }
-    }
-}
-
-// Shared-memory carve-up (dynamic): rotation blocks, boundaries, row tile, slot images.
 struct CompressSmem {
-    float* rot;      // 32*16
-    float* bnd;      // 2*16
-    float* rows;     // kCompressThreads * kRowPitch
-    uint8_t* stage;  // tokens_per_cta * total_bytes   (store variant only)
+    float rot[32 * 16];                          // [block][out j][in k]
+    float bnd[2][16];                            // K and V boundaries, padded with +inf
+    float sq[kRowsPerCta][16][8];                // squares of every row, [thread c][lane l]
 };
-__device__ __forceinline__ CompressSmem carve(uint8_t* base) {
-    CompressSmem s;
-    s.rot = reinterpret_cast<float*>(base);
-    s.bnd = s.rot + 32 * 16;
-    s.rows = s.bnd + 32;
-    s.stage = reinterpret_cast<uint8_t*>(s.rows + kCompressThreads * kRowPitch);
-    return s;
-}
-static size_t compress_smem_bytes(int stage_bytes) {
-    return sizeof(float) * (32 * 16 + 32 + kCompressThreads * kRowPitch) + stage_bytes;
-}
 
 __device__ __forceinline__ void load_params(const CompressParams& p, CompressSmem& sm) {
     for (int i = threadIdx.x; i < 32 * 16; i += blockDim.x) {
         const int g = i >> 4, j = (i >> 2) & 3, k = i & 3;
         sm.rot[i] = __ldg(p.rotation + (4 * g + j) * kHeadDim + 4 * g + k);
     }
-    for (int i = threadIdx.x; i < 32; i += blockDim.x) {
-        const int kv = i >> 4, b = i & 15;
-        sm.bnd[i] = (p.bounds[kv] != nullptr && b < p.n_bounds[kv]) ? __ldg(p.bounds[kv] + b)
-                                                                     : __int_as_float(0x7f800000);
+    if (threadIdx.x < 32) {
+        const int kv = threadIdx.x >> 4, b = threadIdx.x & 15;
+        sm.bnd[kv][b] = (p.bounds[kv] != nullptr && b < p.n_bounds[kv])
+                            ? __ldg(p.bounds[kv] + b) : __int_as_float(0x7f800000);
     }
 }
 
-// Copy `rows_used` rows of 128 elements into the fp32 row tile with 16-byte global loads.
-// row_src(r) returns the global address of row r or nullptr for a row that does not exist.
-template <typename T, typename RowSrc>
-__device__ __forceinline__ void stage_rows(float* rows, int rows_used, RowSrc row_src) {
-    constexpr int E = Chunk16<T>::kElems;
-    constexpr int CH = kHeadDim / E;
-    for (int i = threadIdx.x; i < rows_used * CH; i += blockDim.x) {
-        const int r = i / CH, c = i % CH;
-        const T* src = row_src(r);
-        if (src == nullptr) continue;
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + c * E));
-        float f[E];
-        Chunk16<T>::unpack(v, f);
-        float* dst = rows + r * kRowPitch + c * E;
+// Eight consecutive elements of a row as fp32.
+template <typename T>
+__device__ __forceinline__ void load8(const T* src, float* x) {
+    if constexpr (sizeof(T) == 4) {
+        Chunk16<float>::unpack(__ldg(reinterpret_cast<const uint4*>(src)), x);
+        Chunk16<float>::unpack(__ldg(reinterpret_cast<const uint4*>(src) + 1), x + 4);
+    } else {
+        Chunk16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(src)), x);
+    }
+}
+
+// Normalise, rotate and bucketize this thread's two 4-wide blocks; NB boundaries kept in registers.
+template <int NB>
+__device__ __forceinline__ uint32_t quantize_chunk(const float (&x)[8], int j, float denom,
+                                                   const CompressSmem& sm,
+                                                   const float* __restrict__ bnd) {
+    float bd[NB];
 #pragma unroll
-        for (int e = 0; e < E; e += 4)
-            *reinterpret_cast<float4*>(dst + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+    for (int b = 0; b < NB; ++b) bd[b] = bnd[b];
+    uint32_t word = 0;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int g = 2 * j + half;
+        const float x0 = __fdiv_rn(x[4 * half], denom), x1 = __fdiv_rn(x[4 * half + 1], denom);
+        const float x2 = __fdiv_rn(x[4 * half + 2], denom), x3 = __fdiv_rn(x[4 * half + 3], denom);
+        uint32_t idx[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const float4 r = *reinterpret_cast<const float4*>(sm.rot + g * 16 + jj * 4);
+            float acc = __fmul_rn(x0, r.x);
+            acc = __fmaf_rn(x1, r.y, acc);
+            acc = __fmaf_rn(x2, r.z, acc);
+            acc = __fmaf_rn(x3, r.w, acc);
+            uint32_t n = 0;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) n += (bd[b] < acc) ? 1u : 0u;
+            idx[jj] = n;
+        }
+        const uint32_t b0 = (idx[0] << 4) | idx[1];
+        const uint32_t b1 = (idx[2] << 4) | idx[3];
+        word |= (b0 | (b1 << 8)) << (16 * half);
     }
+    return word;
 }
 
+// The 16 threads of a row: returns this thread's packed word (8 indices) and the row norm.
+// `x` are the thread's elements 8j..8j+7; all 32 lanes of the warp must call this.
+__device__ __forceinline__ uint32_t compress_chunk(const float (&x)[8], int row_in_cta, int j,
+                                                   CompressSmem& sm, const float* __restrict__ bnd,
+                                                   int nb, float& norm_out) {
+    // squares, published for the in-order lane sums
+    float* mine = sm.sq[row_in_cta][j];
+    *reinterpret_cast<float4*>(mine) = make_float4(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]),
+                                                   __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
+    *reinterpret_cast<float4*>(mine + 4) = make_float4(__fmul_rn(x[4], x[4]), __fmul_rn(x[5], x[5]),
+                                                       __fmul_rn(x[6], x[6]), __fmul_rn(x[7], x[7]));
+    __syncwarp();
+    float s = 0.0f;
+    if (j < 8) {
+        s = sm.sq[row_in_cta][0][j];
+#pragma unroll
+        for (int c = 1; c < 16; ++c) s = __fadd_rn(s, sm.sq[row_in_cta][c][j]);
+    }
+    float tot = __shfl_sync(0xffffffffu, s, 0, 16);
+#pragma unroll
+    for (int l = 1; l < 8; ++l) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, s, l, 16));
+    const float norm = __fsqrt_rn(tot);
+    norm_out = norm;
+    const float denom = __fadd_rn(norm, 1e-10f);
+
+    return nb <= 7 ? quantize_chunk<7>(x, j, denom, sm, bnd) : quantize_chunk<15>(x, j, denom, sm, bnd);
+}
+
+// Store variant: rows are ordered (K|V, token, head) so that the two rows of a warp normally use
+// the same codebook; every row's 16 threads write its 64 index bytes and its norm straight into
+// the token's cache slot, and the K row of head 0 also zeroes the slot's padding.
 template <typename T>
 __global__ void __launch_bounds__(kCompressThreads)
 compress_store_kernel(const CompressParams p) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    CompressSmem sm = carve(smem_raw);
-    const int H = p.H;
-    const int tpc = p.tokens_per_cta;
-    const SlotLayout lay = slot_layout(H);
-    const int64_t t0 = static_cast<int64_t>(blockIdx.x) * tpc;
-    const int n_tok = static_cast<int>(min(static_cast<int64_t>(tpc), p.num_tokens - t0));
-
+    __shared__ CompressSmem sm;
     load_params(p, sm);
-    if (p.write_padding) {   // the tail of every slot image is zero
-        const int pad = lay.total - lay.payload_end;
-        for (int i = threadIdx.x; i < n_tok * (pad / 8); i += blockDim.x) {
-            const int tl = i / (pad / 8), o = i % (pad / 8);
-            *reinterpret_cast<uint2*>(sm.stage + tl * lay.total + lay.payload_end + 8 * o) =
-                make_uint2(0u, 0u);
-        }
-    }
-
-    // Rows of this CTA, K rows first: r = kv * (n_tok*H) + tl*H + h; passes of 128 rows.
-    const int rows_total = 2 * n_tok * H;
-    for (int r0 = 0; r0 < rows_total; r0 += kCompressThreads) {
-        const int rows_used = min(kCompressThreads, rows_total - r0);
-        __syncthreads();
-        stage_rows<T>(sm.rows, rows_used, [&](int r) -> const T* {
-            const int rr = r0 + r;
-            const int kv = rr / (n_tok * H), rem = rr % (n_tok * H);
-            const int tl = rem / H, h = rem % H;
-            return static_cast<const T*>(p.src[kv]) + (t0 + tl) * p.token_stride[kv] +
-                   static_cast<int64_t>(h) * p.head_stride[kv];
-        });
-        __syncthreads();
-        if (threadIdx.x < rows_used) {
-            const int rr = r0 + threadIdx.x;
-            const int kv = rr / (n_tok * H), rem = rr % (n_tok * H);
-            const int tl = rem / H, h = rem % H;
-            float norm;
-            uint8_t* slot = sm.stage + tl * lay.total;
-            uint32_t* dst = reinterpret_cast<uint32_t*>(slot + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim);
-            compress_row(sm.rows + threadIdx.x * kRowPitch, sm.rot, sm.bnd + 16 * kv,
-                         p.n_bounds[kv], dst, (lay.v_idx % 16) == 0, norm);
-            *reinterpret_cast<float*>(slot + (kv ? lay.v_norm : lay.k_norm) + 4 * h) = norm;
-        }
-    }
     __syncthreads();
+    const int H = p.H;
+    const SlotLayout lay = slot_layout(H);
+    const int64_t rows_per_kind = p.num_tokens * H;
+    const int row_in_cta = threadIdx.x >> 4, j = threadIdx.x & 15;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + row_in_cta;
+    const bool live = r < 2 * rows_per_kind;
+    const int64_t rr = live ? r : 0;           // dead rows compute on row 0 and store nothing
+    const int kv = static_cast<int>(rr / rows_per_kind);
+    const int64_t rem = rr % rows_per_kind;
+    const int64_t token = rem / H;
+    const int h = static_cast<int>(rem % H);
 
-    // Scatter whole slot images with coalesced 8-byte stores.
-    const int nbytes = p.write_padding ? lay.total : lay.payload_end;
-    const int units = nbytes / 8;
-    for (int i = threadIdx.x; i < n_tok * units; i += blockDim.x) {
-        const int tl = i / units, o = i % units;
-        const int64_t slot = __ldg(p.slot_mapping + t0 + tl);
-        if (slot < 0 || slot >= p.num_slots) continue;
-        const uint2 v = *reinterpret_cast<const uint2*>(sm.stage + tl * lay.total + 8 * o);
-        *reinterpret_cast<uint2*>(p.cache + slot * p.total_bytes + 8 * o) = v;
+    float x[8];
+    load8<T>(static_cast<const T*>(p.src[kv]) + token * p.token_stride[kv] +
+                 static_cast<int64_t>(h) * p.head_stride[kv] + 8 * j, x);
+    float norm;
+    const uint32_t word = compress_chunk(x, row_in_cta, j, sm, sm.bnd[kv], p.n_bounds[kv], norm);
+    if (!live) return;
+    const int64_t slot = __ldg(p.slot_mapping + token);
+    if (slot < 0 || slot >= p.num_slots) return;
+    uint8_t* dst = p.cache + slot * p.total_bytes;
+    *reinterpret_cast<uint32_t*>(dst + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim + 4 * j) = word;
+    if (j == 0) *reinterpret_cast<float*>(dst + (kv ? lay.v_norm : lay.k_norm) + 4 * h) = norm;
+    if (p.write_padding && kv == 0 && h == 0) {
+        const int units = (lay.total - lay.payload_end) / 8;
+        for (int u = j; u < units; u += 16)
+            *reinterpret_cast<uint2*>(dst + lay.payload_end + 8 * u) = make_uint2(0u, 0u);
     }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kCompressThreads)
 compress_rows_kernel(const CompressParams p) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    CompressSmem sm = carve(smem_raw);
+    __shared__ CompressSmem sm;
     load_params(p, sm);
-    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * kCompressThreads;
-    const int64_t left = p.num_tokens - r0;
-    const int rows_used = left < kCompressThreads ? static_cast<int>(left) : kCompressThreads;
-    stage_rows<T>(sm.rows, rows_used, [&](int r) -> const T* {
-        return static_cast<const T*>(p.src[0]) + (r0 + r) * p.token_stride[0];
-    });
     __syncthreads();
-    if (threadIdx.x < rows_used) {
-        float norm;
-        uint32_t* dst = reinterpret_cast<uint32_t*>(p.packed_out + (r0 + threadIdx.x) * kHalfDim);
-        compress_row(sm.rows + threadIdx.x * kRowPitch, sm.rot, sm.bnd, p.n_bounds[0], dst, true, norm);
-        p.norms_out[r0 + threadIdx.x] = norm;
-    }
+    const int row_in_cta = threadIdx.x >> 4, j = threadIdx.x & 15;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + row_in_cta;
+    const bool live = r < p.num_tokens;
+    const int64_t rr = live ? r : 0;
+    float x[8];
+    load8<T>(static_cast<const T*>(p.src[0]) + rr * p.token_stride[0] + 8 * j, x);
+    float norm;
+    const uint32_t word = compress_chunk(x, row_in_cta, j, sm, sm.bnd[0], p.n_bounds[0], norm);
+    if (!live) return;
+    reinterpret_cast<uint32_t*>(p.packed_out + r * kHalfDim)[j] = word;
+    if (j == 0) p.norms_out[r] = norm;
 }
 
 // ---- decompress ------------------------------------------------------------
@@ -303,6 +255,18 @@ static int check_bounds_count(int n, const char* what) {
     return RQ_OK;
 }
 
+template <typename T>
+static void launch_store(const CompressParams& p, cudaStream_t st) {
+    const int64_t rows = 2 * p.num_tokens * p.H;
+    const unsigned grid = static_cast<unsigned>((rows + kRowsPerCta - 1) / kRowsPerCta);
+    compress_store_kernel<T><<<grid, kCompressThreads, 0, st>>>(p);
+}
+template <typename T>
+static void launch_rows(const CompressParams& p, cudaStream_t st) {
+    const unsigned grid = static_cast<unsigned>((p.num_tokens + kRowsPerCta - 1) / kRowsPerCta);
+    compress_rows_kernel<T><<<grid, kCompressThreads, 0, st>>>(p);
+}
+
 }  // namespace rq
 
 using namespace rq;
@@ -337,6 +301,8 @@ extern "C" int rq_compress_store(const void* key, const void* value, int in_dtyp
                         static_cast<long long>(s));
     if (!aligned(key, 16) || !aligned(value, 16) || !aligned(kv_cache, 16))
         return fail(RQ_ERR_ALIGNMENT, "rq_compress_store: key/value/kv_cache must be 16-byte aligned");
+    if (2 * num_tokens * num_kv_heads / kRowsPerCta >= 0x7fffffffLL)
+        return fail(RQ_ERR_UNSUPPORTED, "rq_compress_store: too many rows for one launch");
 
     CompressParams p{};
     p.src[0] = key; p.src[1] = value;
@@ -348,28 +314,11 @@ extern "C" int rq_compress_store(const void* key, const void* value, int in_dtyp
     p.rotation = rotation;
     p.bounds[0] = k_boundaries; p.bounds[1] = v_boundaries;
     p.n_bounds[0] = n_k_boundaries; p.n_bounds[1] = n_v_boundaries;
-    int tpc = kCompressThreads / (2 * num_kv_heads);
-    if (tpc < 1) tpc = 1;
-    p.tokens_per_cta = tpc;
-    const size_t smem = compress_smem_bytes(tpc * total_bytes);
-    if (smem > 200 * 1024)
-        return fail(RQ_ERR_UNSUPPORTED, "rq_compress_store: %d KV heads need too much shared memory",
-                    num_kv_heads);
-    const unsigned grid = static_cast<unsigned>((num_tokens + tpc - 1) / tpc);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (in_dtype) {
-        case RQ_DTYPE_F32:
-            if (int e = ensure_smem(compress_store_kernel<float>, smem)) return e;
-            compress_store_kernel<float><<<grid, kCompressThreads, smem, st>>>(p);
-            break;
-        case RQ_DTYPE_F16:
-            if (int e = ensure_smem(compress_store_kernel<__half>, smem)) return e;
-            compress_store_kernel<__half><<<grid, kCompressThreads, smem, st>>>(p);
-            break;
-        default:
-            if (int e = ensure_smem(compress_store_kernel<__nv_bfloat16>, smem)) return e;
-            compress_store_kernel<__nv_bfloat16><<<grid, kCompressThreads, smem, st>>>(p);
-            break;
+        case RQ_DTYPE_F32: launch_store<float>(p, st); break;
+        case RQ_DTYPE_F16: launch_store<__half>(p, st); break;
+        default: launch_store<__nv_bfloat16>(p, st); break;
     }
     return check_cuda(cudaGetLastError(), "rq_compress_store launch");
 }
@@ -386,28 +335,17 @@ extern "C" int rq_compress(const void* x, int in_dtype, int64_t num_rows, int he
     if (num_rows == 0) return RQ_OK;
     if (!x || !rotation || !boundaries || !packed_out || !norms_out)
         return fail(RQ_ERR_INVALID_ARG, "rq_compress: null pointer");
-    if ((row_stride * dtype_bytes(in_dtype)) % 16 != 0 || !aligned(x, 16) || !aligned(packed_out, 16))
-        return fail(RQ_ERR_ALIGNMENT, "rq_compress: rows and packed_out must be 16-byte aligned");
+    if ((row_stride * dtype_bytes(in_dtype)) % 16 != 0 || !aligned(x, 16) || !aligned(packed_out, 4))
+        return fail(RQ_ERR_ALIGNMENT, "rq_compress: rows must be 16-byte aligned");
     CompressParams p{};
     p.src[0] = x; p.token_stride[0] = row_stride; p.num_tokens = num_rows;
     p.packed_out = packed_out; p.norms_out = norms_out; p.rotation = rotation;
     p.bounds[0] = boundaries; p.n_bounds[0] = n_boundaries;
-    const size_t smem = compress_smem_bytes(0);
-    const unsigned grid = static_cast<unsigned>((num_rows + kCompressThreads - 1) / kCompressThreads);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (in_dtype) {
-        case RQ_DTYPE_F32:
-            if (int e = ensure_smem(compress_rows_kernel<float>, smem)) return e;
-            compress_rows_kernel<float><<<grid, kCompressThreads, smem, st>>>(p);
-            break;
-        case RQ_DTYPE_F16:
-            if (int e = ensure_smem(compress_rows_kernel<__half>, smem)) return e;
-            compress_rows_kernel<__half><<<grid, kCompressThreads, smem, st>>>(p);
-            break;
-        default:
-            if (int e = ensure_smem(compress_rows_kernel<__nv_bfloat16>, smem)) return e;
-            compress_rows_kernel<__nv_bfloat16><<<grid, kCompressThreads, smem, st>>>(p);
-            break;
+        case RQ_DTYPE_F32: launch_rows<float>(p, st); break;
+        case RQ_DTYPE_F16: launch_rows<__half>(p, st); break;
+        default: launch_rows<__nv_bfloat16>(p, st); break;
     }
     return check_cuda(cudaGetLastError(), "rq_compress launch");
 }

@@ -27,7 +27,7 @@ namespace rq {
 constexpr int kDecodeWarps = 8;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kTile = 16;                 // tokens per tile (one mma k-step of P@V)
-constexpr int kStages = 4;                // cp.async ring depth per warp
+constexpr int kStages = 3;                // cp.async ring depth per warp
 constexpr int kVPitch = 80;               // bytes per token row of V indices in smem (64 + pad)
 constexpr int kHeadsPerCta = 8;           // query heads handled per CTA (mma N of P@V)
 
@@ -84,7 +84,7 @@ template <>
 __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1,
                                                         uint32_t a2, uint32_t a3, uint32_t b0,
                                                         uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
         "{%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -94,7 +94,7 @@ template <>
 __device__ __forceinline__ void mma16816<__half>(float (&d)[4], uint32_t a0, uint32_t a1,
                                                  uint32_t a2, uint32_t a3, uint32_t b0,
                                                  uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
         "{%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -142,8 +142,14 @@ __device__ __forceinline__ void store_rounded(__half* dst, float v) { *dst = __f
 
 // ---- per-token lookup tables -------------------------------------------------
 //
-// A table holds round_T(centroid[i] * norm) for i < 2^BITS, split into a low-byte plane and a
-// high-byte plane so that one PRMT fetches the bytes of four nibble indices at once.
+// Every (token, K|V) gets a table of its 2^BITS decompressed values round_T(centroid[i] * norm),
+// stored as byte planes so that one PRMT fetches the bytes of four nibble indices at once.
+//
+// V tables hold the T (bf16/f16) bit patterns: a low-byte plane and a high-byte plane.
+// K tables hold the same values as 15-bit integers I[i] = value * 2^(13 - e), e the exponent of
+// the largest entry (exact unless the entries span more than 6 binades), split into two signed
+// byte planes I = 256 * hi + lo, plus the scale 2^(e - 13).  Q K^T then runs on the int8 tensor
+// path, which needs half the PRMTs of a 16-bit operand.
 //   BITS == 3: 4 registers  {lo[0..3], lo[4..7], hi[0..3], hi[4..7]}
 //   BITS == 4: 8 registers  {lo[0..3] .. lo[12..15], hi[0..3] .. hi[12..15]}
 template <int BITS>
@@ -152,60 +158,151 @@ struct Table {
     uint32_t r[kRegs];
 };
 
-template <typename T, int BITS>
-__device__ __forceinline__ Table<BITS> build_table(const float* __restrict__ cb, float norm) {
-    constexpr int N = 1 << BITS;
-    uint32_t pairs[N / 2];
+// Power of two 2^k as a float, k in [-126, 127].
+__device__ __forceinline__ float pow2i(int k) { return __int_as_float((k + 127) << 23); }
+
+// Exponent e with 2^e <= v < 2^(e+1) for a finite normal v > 0.
+__device__ __forceinline__ int exponent_of(float v) { return ((__float_as_int(v) >> 23) & 0xFF) - 127; }
+
+// Half of a token's tables, built by one lane; lanes l and l ^ 16 hold the two halves of a token.
+// NH = entries in this half (4 or 8); planes come out as NH/4 registers each.
+template <typename T, int NH>
+__device__ __forceinline__ void build_half_value_table(const float* __restrict__ cb_half, float norm,
+                                                       uint32_t* lo, uint32_t* hi) {
+    uint32_t pairs[NH / 2];
 #pragma unroll
-    for (int i = 0; i < N / 2; ++i)
-        pairs[i] = pack_pair<T>(__fmul_rn(cb[2 * i], norm), __fmul_rn(cb[2 * i + 1], norm));
+    for (int i = 0; i < NH / 2; ++i)
+        pairs[i] = pack_pair<T>(__fmul_rn(cb_half[2 * i], norm), __fmul_rn(cb_half[2 * i + 1], norm));
+#pragma unroll
+    for (int i = 0; i < NH / 4; ++i) {
+        lo[i] = prmt(pairs[2 * i], pairs[2 * i + 1], 0x6420);
+        hi[i] = prmt(pairs[2 * i], pairs[2 * i + 1], 0x7531);
+    }
+}
+
+template <typename T, int NH>
+__device__ __forceinline__ void build_half_int_table(const float* __restrict__ cb_half, float norm,
+                                                     uint32_t* lo, uint32_t* hi, float& unscale) {
+    float v[NH];
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NH; ++i) {
+        v[i] = round_to<T>(__fmul_rn(cb_half[i], norm));
+        mx = fmaxf(mx, fabsf(v[i]));
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));      // maximum over the whole table
+    const bool ok = mx >= 1.0e-30f && mx <= 3.0e38f;
+    const int e = ok ? exponent_of(mx) : 0;
+    const float scale = ok ? pow2i(13 - e) : 0.0f;
+    unscale = ok ? pow2i(e - 13) : 0.0f;
+    int u[NH];
+#pragma unroll
+    for (int i = 0; i < NH; ++i) u[i] = __float2int_rn(fmaf(v[i], scale, 128.0f));
+#pragma unroll
+    for (int i = 0; i < NH / 4; ++i) {
+        const uint32_t a = prmt(u[4 * i], u[4 * i + 1], 0x5140);
+        const uint32_t b = prmt(u[4 * i + 2], u[4 * i + 3], 0x5140);
+        lo[i] = prmt(a, b, 0x5410) ^ 0x80808080u;
+        hi[i] = prmt(a, b, 0x7632);
+    }
+}
+
+// Bytes of the four entries selected by the four nibbles in sel[15:0] from one byte plane
+// (plane = N/4 registers).
+template <int BITS>
+__device__ __forceinline__ uint32_t lookup_plane(const uint32_t* plane, uint32_t sel, uint32_t s7,
+                                                 uint32_t m) {
+    if constexpr (BITS == 3) {
+        return prmt(plane[0], plane[1], sel);
+    } else {
+        const uint32_t a = prmt(plane[0], plane[1], s7), b = prmt(plane[2], plane[3], s7);
+        return (a & ~m) | (b & m);
+    }
+}
+
+// Lookup of both planes for the nibbles in sel[15:0].
+template <int BITS>
+__device__ __forceinline__ void lookup4(const Table<BITS>& t, uint32_t sel, uint32_t& lo,
+                                        uint32_t& hi) {
+    uint32_t s7 = 0, m = 0;
+    if constexpr (BITS == 4) {
+        s7 = sel & 0x7777u;
+        const uint32_t y = prmt(sel, sel << 4, 0x5410);
+        m = prmt(y, y, 0x9B8A);      // byte i = 0xFF when nibble i of sel has its top bit set
+    }
+    lo = lookup_plane<BITS>(&t.r[0], sel, s7, m);
+    hi = lookup_plane<BITS>(&t.r[Table<BITS>::kRegs / 2], sel, s7, m);
+}
+
+template <int BITS>
+__device__ __forceinline__ void store_table(uint32_t* dst, const Table<BITS>& t) {
+#pragma unroll
+    for (int r4 = 0; r4 < Table<BITS>::kRegs / 4; ++r4)
+        *reinterpret_cast<uint4*>(dst + 4 * r4) =
+            make_uint4(t.r[4 * r4], t.r[4 * r4 + 1], t.r[4 * r4 + 2], t.r[4 * r4 + 3]);
+}
+template <int BITS>
+__device__ __forceinline__ Table<BITS> load_table(const uint32_t* src) {
     Table<BITS> t;
 #pragma unroll
-    for (int i = 0; i < N / 4; ++i) {
-        t.r[i] = prmt(pairs[2 * i], pairs[2 * i + 1], 0x6420);             // low bytes
-        t.r[N / 4 + i] = prmt(pairs[2 * i], pairs[2 * i + 1], 0x7531);     // high bytes
+    for (int r4 = 0; r4 < Table<BITS>::kRegs / 4; ++r4) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src + 4 * r4);
+        t.r[4 * r4] = v.x; t.r[4 * r4 + 1] = v.y; t.r[4 * r4 + 2] = v.z; t.r[4 * r4 + 3] = v.w;
     }
     return t;
 }
 
-// Bytes of the four entries selected by the four nibbles in sel[15:0]: lo plane and hi plane.
-template <int BITS>
-__device__ __forceinline__ void lookup4(const Table<BITS>& t, uint32_t sel, uint32_t& lo,
-                                        uint32_t& hi) {
-    if constexpr (BITS == 3) {
-        lo = prmt(t.r[0], t.r[1], sel);
-        hi = prmt(t.r[2], t.r[3], sel);
-    } else {
-        const uint32_t s7 = sel & 0x7777u;
-        // byte i of `m` is 0xFF when nibble i of sel has its top bit set
-        const uint32_t y = prmt(sel, sel << 4, 0x5410);
-        const uint32_t m = prmt(y, y, 0x9B8A);
-        const uint32_t la = prmt(t.r[0], t.r[1], s7), lb = prmt(t.r[2], t.r[3], s7);
-        const uint32_t ha = prmt(t.r[4], t.r[5], s7), hb = prmt(t.r[6], t.r[7], s7);
-        lo = (la & ~m) | (lb & m);
-        hi = (ha & ~m) | (hb & m);
-    }
+// int8 tensor-core MMA, D(16x8,s32) += A(16x32,s8) * B(32x8,s8).
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                       uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr));
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 // ---- shared memory ------------------------------------------------------------
 
 struct __align__(16) Stage {
     uint8_t k[kTile][kHalfDim];        // K indices of 16 tokens
-    uint8_t v[kTile][kVPitch];         // V indices, padded rows (conflict-free 8-byte reads)
+    uint8_t v[kTile][kVPitch];         // V indices, padded rows (conflict-free 16-byte reads)
     float norms[2 * kTile];            // [0..15] K norms, [16..31] V norms
 };
-struct __align__(16) WarpSmem {
+struct __align__(256) WarpSmem {
+    uint16_t vt[kTile][kHeadDim];      // decompressed V tile, 16-byte chunks XOR-swizzled by token
     Stage stage[kStages];
-    uint32_t tbl_k[kTile][8];          // per-token K tables (4 or 8 registers used)
-    uint32_t tbl_v[kTile][8];
+    uint32_t tbl_k[kTile][8];          // per-token K integer planes (4 or 8 registers used)
+    uint32_t tbl_v[kTile][8];          // per-token V value planes
+    float k_unscale[kTile];            // 2^(e-13) of every K table
 };
 static_assert(sizeof(WarpSmem) >= sizeof(float) * (kHeadsPerCta * kHeadDim + 2 * kHeadsPerCta),
               "the per-warp area is reused for the cross-warp merge");
 
-struct __align__(16) DecodeSmem {
+struct __align__(256) DecodeSmem {
     WarpSmem warp[kDecodeWarps];
-    uint16_t q[kHeadsPerCta][kHeadDim];   // rotated queries, element d stored at d ^ 1
-    float cb[2][16];                      // K and V codebooks
+    uint8_t q_hi[kHeadsPerCta][kHeadDim];   // signed byte planes of the rotated queries' integer
+    uint8_t q_lo[kHeadsPerCta][kHeadDim];   // image (256 * hi + lo); element d stored at index d ^ 1
+    float q_unscale[kHeadsPerCta];
+    float cb[2][16];                         // K and V codebooks
 };
 
 // ---- the split kernel -------------------------------------------------------------
@@ -213,7 +310,7 @@ struct __align__(16) DecodeSmem {
 template <typename T, int KB, int VB>
 __global__ void __launch_bounds__(kDecodeThreads, 2)
 decode_split_kernel(const DecodeParams p) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(256) uint8_t smem_raw[];
     DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(smem_raw);
 
     const int split = blockIdx.x;
@@ -233,51 +330,6 @@ decode_split_kernel(const DecodeParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tig = lane & 3;
 
-    // ---- prologue: codebooks, q_rot = round(q @ R^T) into shared memory ----
-    if (tid < 32) {
-        const int kv = tid >> 4, i = tid & 15;
-        const int n = kv ? (1 << VB) : (1 << KB);
-        sm.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
-    }
-    {
-        // 8 heads x 32 blocks of four = 256 work items, one per thread
-        const int h = tid >> 5, blk = tid & 31;
-        float r[4] = {0.f, 0.f, 0.f, 0.f};
-        if (h < heads_here) {
-            const T* qp = static_cast<const T*>(p.q) + seq * p.q_stride_seq +
-                          static_cast<int64_t>(first_qh + h) * p.q_stride_head + 4 * blk;
-            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(qp));
-            const float2 x01 = unpack_pair<T>(raw.x), x23 = unpack_pair<T>(raw.y);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float4 rr = __ldg(reinterpret_cast<const float4*>(
-                    p.rotation + (4 * blk + j) * kHeadDim + 4 * blk));
-                float acc = __fmul_rn(x01.x, rr.x);
-                acc = __fmaf_rn(x01.y, rr.y, acc);
-                acc = __fmaf_rn(x23.x, rr.z, acc);
-                acc = __fmaf_rn(x23.y, rr.w, acc);
-                r[j] = acc;
-            }
-        }
-        // element d lives at index d ^ 1: (r1, r0, r3, r2)
-        uint2 st;
-        st.x = pack_pair<T>(r[1], r[0]);
-        st.y = pack_pair<T>(r[3], r[2]);
-        *reinterpret_cast<uint2*>(&sm.q[h][4 * blk]) = st;
-    }
-    __syncthreads();
-
-    // Query fragments (mma A operand, rows = heads, upper 8 rows are zero).  For k-step
-    // ks = 2w + e the thread supplies k-slots {2tig,2tig+1} and {2tig+8,2tig+9}, which this
-    // kernel maps to the elements of nibbles 4e..4e+3 of word w of the thread's 16-byte chunk.
-    uint32_t qa[8][2];
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-        const int off = 32 * tig + 8 * (ks >> 1) + 4 * (ks & 1);
-        qa[ks][0] = *reinterpret_cast<const uint32_t*>(&sm.q[g][off]);
-        qa[ks][1] = *reinterpret_cast<const uint32_t*>(&sm.q[g][off + 2]);
-    }
-
     // ---- per-warp streaming state ----
     WarpSmem& ws = sm.warp[warp];
     const SlotLayout lay = slot_layout(p.H);
@@ -285,52 +337,71 @@ decode_split_kernel(const DecodeParams p) {
     const int32_t* bt_row = p.block_table + seq * p.bt_stride;
     const int v_align = (lay.v_idx % 16 == 0) ? 16 : ((lay.v_idx % 8 == 0) ? 8 : 4);
 
-    auto phys_slot0 = [&](int tile) -> int64_t {      // slot of the tile's first token (fast path)
-        const int t0 = tile * kTile;
-        int64_t blk = __ldg(bt_row + t0 / p.block_size);
-        blk = blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
-        return blk * p.block_size + (t0 % p.block_size);
+    auto clamp_block = [&](int64_t blk) -> int64_t {
+        return blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
     };
-    auto token_slot = [&](int tile, int i, int64_t slot0) -> int64_t {
-        if (fast_bt) return slot0 + i;
-        int t = tile * kTile + i;
-        t = min(t, seq_len - 1);
-        int64_t blk = __ldg(bt_row + t / p.block_size);
-        blk = blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
-        return blk * p.block_size + (t % p.block_size);
+    // fast path (block_size a multiple of 16): the 16 slots of a tile are contiguous
+    auto phys_slot0 = [&](int tile) -> int64_t {
+        const int t0 = tile * kTile;
+        return clamp_block(__ldg(bt_row + t0 / p.block_size)) * p.block_size + (t0 % p.block_size);
+    };
+    auto token_slot = [&](int tile, int i) -> int64_t {      // general path: one lookup per token
+        const int t = min(tile * kTile + i, seq_len - 1);
+        return clamp_block(__ldg(bt_row + t / p.block_size)) * p.block_size + (t % p.block_size);
     };
 
+    // Per-lane source offsets (bytes from the tile's first slot) and shared-memory destinations
+    // (bytes from the stage) of this lane's copies; fixed for the whole kernel.
+    const uint32_t tb = static_cast<uint32_t>(p.total_bytes);
+    const uint32_t src_k = (lane >> 2) * tb + kvh * kHalfDim + 16 * (lane & 3);      // + 8*tb for copy 2
+    const uint32_t dst_k = (lane >> 2) * kHalfDim + 16 * (lane & 3);
+    const uint32_t dst_v16 = sizeof(Stage::k) + (lane >> 2) * kVPitch + 16 * (lane & 3);
+    const uint32_t src_n = (lane & 15) * tb + ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh;
+    const uint32_t dst_n = sizeof(Stage::k) + sizeof(Stage::v) + 4 * lane;
+
     auto issue = [&](int tile, int s, int64_t slot0) {
-        Stage& st = ws.stage[s];
+        uint8_t* stg = reinterpret_cast<uint8_t*>(&ws.stage[s]);
+        if (fast_bt) {
+            const uint8_t* base = p.cache + slot0 * p.total_bytes;
+            cp_async16(stg + dst_k, base + src_k);
+            cp_async16(stg + dst_k + 8 * kHalfDim, base + src_k + 8 * tb);
+            if (v_align == 16) {
+                cp_async16(stg + dst_v16, base + src_k + lay.v_idx);
+                cp_async16(stg + dst_v16 + 8 * kVPitch, base + src_k + 8 * tb + lay.v_idx);
+            } else if (v_align == 8) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = lane + 32 * j, i = c >> 3, part = c & 7;
+                    cp_async8(stg + sizeof(Stage::k) + i * kVPitch + 8 * part,
+                              base + i * tb + lay.v_idx + kvh * kHalfDim + 8 * part);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int c = lane + 32 * j, i = c >> 4, part = c & 15;
+                    cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
+                              base + i * tb + lay.v_idx + kvh * kHalfDim + 4 * part);
+                }
+            }
+            cp_async4(stg + dst_n, base + src_n);
+            return;
+        }
+        // general path: tokens of a tile may sit in different blocks
         const uint8_t* head_base = p.cache + kvh * kHalfDim;
-        // K indices: 64 chunks of 16 bytes, two per lane
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int c = lane + 32 * j, i = c >> 2, part = c & 3;
-            const uint8_t* src = head_base + token_slot(tile, i, slot0) * p.total_bytes + 16 * part;
-            cp_async16(&st.k[i][16 * part], src + lay.k_idx);
-            if (v_align == 16) cp_async16(&st.v[i][16 * part], src + lay.v_idx);
+            const uint8_t* src = head_base + token_slot(tile, i) * p.total_bytes + 16 * part;
+            cp_async16(stg + i * kHalfDim + 16 * part, src + lay.k_idx);
         }
-        if (v_align == 8) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int c = lane + 32 * j, i = c >> 3, part = c & 7;
-                cp_async8(&st.v[i][8 * part], head_base + token_slot(tile, i, slot0) * p.total_bytes +
-                                                  lay.v_idx + 8 * part);
-            }
-        } else if (v_align == 4) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int c = lane + 32 * j, i = c >> 4, part = c & 15;
-                cp_async4(&st.v[i][4 * part], head_base + token_slot(tile, i, slot0) * p.total_bytes +
-                                                  lay.v_idx + 4 * part);
-            }
+        for (int j = 0; j < 8; ++j) {
+            const int c = lane + 32 * j, i = c >> 4, part = c & 15;
+            cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
+                      head_base + token_slot(tile, i) * p.total_bytes + lay.v_idx + 4 * part);
         }
-        {   // norms: lanes 0..15 K, 16..31 V
-            const int i = lane & 15, kv = lane >> 4;
-            cp_async4(&st.norms[lane], p.cache + token_slot(tile, i, slot0) * p.total_bytes +
-                                           (kv ? lay.v_norm : lay.k_norm) + 4 * kvh);
-        }
+        cp_async4(stg + dst_n, p.cache + token_slot(tile, lane & 15) * p.total_bytes +
+                                   ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh);
     };
 
     // online-softmax state of head g (partial over this thread's token columns)
@@ -345,13 +416,14 @@ decode_split_kernel(const DecodeParams p) {
     const int n_my = first_tile < tile_end ? (tile_end - first_tile + kDecodeWarps - 1) / kDecodeWarps : 0;
 
     // prefetch pipeline: block-table entry of the next tile to issue is read one step ahead
-    int pf_it = 0;
+    int pf_it = 0, pf_stage = 0;
     int64_t pf_slot0 = (n_my > 0 && fast_bt) ? phys_slot0(first_tile) : 0;
     auto issue_next = [&]() {
         if (pf_it < n_my) {
             const int tile = first_tile + pf_it * kDecodeWarps;
-            issue(tile, pf_it % kStages, pf_slot0);
+            issue(tile, pf_stage, pf_slot0);
             ++pf_it;
+            pf_stage = pf_stage + 1 == kStages ? 0 : pf_stage + 1;
             if (pf_it < n_my && fast_bt) pf_slot0 = phys_slot0(first_tile + pf_it * kDecodeWarps);
         }
         cp_async_commit();
@@ -359,80 +431,161 @@ decode_split_kernel(const DecodeParams p) {
 #pragma unroll 1
     for (int s = 0; s < kStages - 1; ++s) issue_next();
 
+    // (the first tiles are now in flight; their latency overlaps the query set-up below)
+    // ---- prologue: codebooks; q_rot = round_T(q @ R^T) as int16 planes in shared memory ----
+    if (tid < 32) {
+        const int kv = tid >> 4, i = tid & 15;
+        const int n = kv ? (1 << VB) : (1 << KB);
+        sm.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
+    }
+    {
+        // warp h rotates head h: lane = one 4x4 block
+        const int h = warp, blk = lane;
+        float r[4] = {0.f, 0.f, 0.f, 0.f};
+        if (h < heads_here) {
+            const T* qp = static_cast<const T*>(p.q) + seq * p.q_stride_seq +
+                          static_cast<int64_t>(first_qh + h) * p.q_stride_head + 4 * blk;
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(qp));
+            const float2 x01 = unpack_pair<T>(raw.x), x23 = unpack_pair<T>(raw.y);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 rr = __ldg(reinterpret_cast<const float4*>(
+                    p.rotation + (4 * blk + j) * kHeadDim + 4 * blk));
+                float acc = __fmul_rn(x01.x, rr.x);
+                acc = __fmaf_rn(x01.y, rr.y, acc);
+                acc = __fmaf_rn(x23.x, rr.z, acc);
+                acc = __fmaf_rn(x23.y, rr.w, acc);
+                r[j] = round_to<T>(acc);
+            }
+        }
+        float mx = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const bool ok = mx >= 1.0e-30f && mx <= 3.0e38f;
+        const int e = ok ? exponent_of(mx) : 0;
+        const float scale = ok ? pow2i(13 - e) : 0.0f;
+        int qu[4];      // integer image + 128: byte 1 = signed high digit, byte 0 ^ 0x80 = signed low digit
+#pragma unroll
+        for (int j = 0; j < 4; ++j) qu[j] = __float2int_rn(fmaf(r[j], scale, 128.0f));
+        // element d lives at index d ^ 1: byte order (1, 0, 3, 2)
+        const uint32_t a = prmt(qu[1], qu[0], 0x5140), b = prmt(qu[3], qu[2], 0x5140);
+        *reinterpret_cast<uint32_t*>(&sm.q_lo[h][4 * blk]) = prmt(a, b, 0x5410) ^ 0x80808080u;
+        *reinterpret_cast<uint32_t*>(&sm.q_hi[h][4 * blk]) = prmt(a, b, 0x7632);
+        if (lane == 0) sm.q_unscale[h] = ok ? pow2i(e - 13) : 0.0f;
+    }
+    __syncthreads();
+
+    // Query fragments (mma A operand): rows 0..7 carry the high digits of heads 0..7, rows 8..15
+    // the low digits of the same heads, so one MMA yields Qhi.K and Qlo.K for a K plane.  In
+    // k-step w the thread supplies k-slots 4tig..4tig+3 and 16+4tig..16+4tig+3, which this kernel
+    // maps to the elements of nibbles 0..3 and 4..7 of word w of its 16-byte chunk of a K row.
+    uint32_t qa[4][4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const int off = 32 * tig + 8 * w;
+        qa[w][0] = *reinterpret_cast<const uint32_t*>(&sm.q_hi[g][off]);
+        qa[w][1] = *reinterpret_cast<const uint32_t*>(&sm.q_lo[g][off]);
+        qa[w][2] = *reinterpret_cast<const uint32_t*>(&sm.q_hi[g][off + 4]);
+        qa[w][3] = *reinterpret_cast<const uint32_t*>(&sm.q_lo[g][off + 4]);
+    }
+    const float q_factor = sm.q_unscale[g] * p.qk_scale;
+
+
+    // per-lane constants of the V transpose: this lane decompresses half a row of token tv ...
+    const int tv = lane & 15, vhalf = lane >> 4;
+    // ... and feeds ldmatrix with row (lane & 7) of 8x8 matrix (lane >> 3)
+    const int lm_tok = (lane & 7) + ((lane & 16) ? 8 : 0);
+    const int lm_chunk = (lane >> 3) & 1;
+    // generic addresses whose low byte already holds the swizzle; chunk selection is one XOR
+    const uint32_t vt_store_base = static_cast<uint32_t>(__cvta_generic_to_shared(&ws.vt[tv][0])) +
+                                   128u * vhalf + 16u * (tv & 7);
+    const uint32_t lm_base = static_cast<uint32_t>(__cvta_generic_to_shared(&ws.vt[lm_tok][0])) +
+                             16u * (lm_chunk ^ (lm_tok & 7));
+
+    int cur_stage = 0;
 #pragma unroll 1
     for (int it = 0; it < n_my; ++it) {
         issue_next();
         cp_async_wait<kStages - 1>();
         __syncwarp();
-        const Stage& st = ws.stage[it % kStages];
+        const Stage& st = ws.stage[cur_stage];
+        cur_stage = cur_stage + 1 == kStages ? 0 : cur_stage + 1;
         const int tile = first_tile + it * kDecodeWarps;
         const int n_valid = min(kTile, seq_len - tile * kTile);
 
-        // ---- per-token tables: lane builds token (lane & 15) of K (lanes 0-15) or V ----
+        // ---- per-token tables: lane builds one half (lane >> 4) of the K and of the V table of
+        //      token (lane & 15), so both half-warps run the same instructions ----
         {
-            const int i = lane & 15;
-            const float norm = i < n_valid ? st.norms[lane] : 0.0f;
-            if (lane < 16) {
-                const Table<KB> t = build_table<T, KB>(sm.cb[0], norm);
+            const int i = lane & 15, hb = lane >> 4;
+            const bool valid = i < n_valid;
+            const float norm_k = valid ? st.norms[i] : 0.0f;
+            const float norm_v = valid ? st.norms[kTile + i] : 0.0f;
+            constexpr int NKH = (1 << KB) / 2, NVH = (1 << VB) / 2;
+            float unscale;
+            uint32_t lo[NKH / 4], hi[NKH / 4];
+            build_half_int_table<T, NKH>(&sm.cb[0][hb * NKH], norm_k, lo, hi, unscale);
+            uint32_t vlo[NVH / 4], vhi[NVH / 4];
+            build_half_value_table<T, NVH>(&sm.cb[1][hb * NVH], norm_v, vlo, vhi);
 #pragma unroll
-                for (int r4 = 0; r4 < Table<KB>::kRegs / 4; ++r4)
-                    *reinterpret_cast<uint4*>(&ws.tbl_k[i][4 * r4]) =
-                        make_uint4(t.r[4 * r4], t.r[4 * r4 + 1], t.r[4 * r4 + 2], t.r[4 * r4 + 3]);
-            } else {
-                const Table<VB> t = build_table<T, VB>(sm.cb[1], norm);
-#pragma unroll
-                for (int r4 = 0; r4 < Table<VB>::kRegs / 4; ++r4)
-                    *reinterpret_cast<uint4*>(&ws.tbl_v[i][4 * r4]) =
-                        make_uint4(t.r[4 * r4], t.r[4 * r4 + 1], t.r[4 * r4 + 2], t.r[4 * r4 + 3]);
+            for (int r = 0; r < NKH / 4; ++r) {
+                ws.tbl_k[i][hb * (NKH / 4) + r] = lo[r];
+                ws.tbl_k[i][2 * (NKH / 4) + hb * (NKH / 4) + r] = hi[r];
             }
+#pragma unroll
+            for (int r = 0; r < NVH / 4; ++r) {
+                ws.tbl_v[i][hb * (NVH / 4) + r] = vlo[r];
+                ws.tbl_v[i][2 * (NVH / 4) + hb * (NVH / 4) + r] = vhi[r];
+            }
+            if (hb == 0) ws.k_unscale[i] = unscale;
         }
         __syncwarp();
 
-        // ---- S = Q K^T : rows = heads (g), columns = tokens; two 8-token column tiles ----
-        float s_acc[2][4];
+        // ---- S = Q K^T on the int8 path: rows = heads (g), columns = tokens ----
+        float sc[4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) s_acc[nt][c] = 0.0f;
+            // acc_h = [Qhi; Qlo] . Khi, acc_l = [Qhi; Qlo] . Klo: entries 0,1 are the Qhi rows,
+            // entries 2,3 the Qlo rows of the same head and the same two tokens
+            int acc_h[4] = {0, 0, 0, 0}, acc_l[4] = {0, 0, 0, 0};
             const int tok = g + 8 * nt;
             const uint4 kw = *reinterpret_cast<const uint4*>(&st.k[tok][16 * tig]);
-            Table<KB> tk;
-#pragma unroll
-            for (int r4 = 0; r4 < Table<KB>::kRegs / 4; ++r4) {
-                const uint4 tv = *reinterpret_cast<const uint4*>(&ws.tbl_k[tok][4 * r4]);
-                tk.r[4 * r4] = tv.x; tk.r[4 * r4 + 1] = tv.y; tk.r[4 * r4 + 2] = tv.z; tk.r[4 * r4 + 3] = tv.w;
-            }
+            const Table<KB> tk = load_table<KB>(ws.tbl_k[tok]);
             const uint32_t words[4] = {kw.x, kw.y, kw.z, kw.w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
+                uint32_t lo0, hi0, lo1, hi1;
+                lookup4<KB>(tk, words[w], lo0, hi0);            // nibbles 0..3 -> k-slots 4tig..
+                lookup4<KB>(tk, words[w] >> 16, lo1, hi1);      // nibbles 4..7 -> k-slots 16+4tig..
+                mma_s8(acc_h, qa[w][0], qa[w][1], qa[w][2], qa[w][3], hi0, hi1);
+                mma_s8(acc_l, qa[w][0], qa[w][1], qa[w][2], qa[w][3], lo0, lo1);
+            }
+            const float2 ku = *reinterpret_cast<const float2*>(&ws.k_unscale[8 * nt + 2 * tig]);
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    uint32_t lo, hi;
-                    lookup4<KB>(tk, e ? (words[w] >> 16) : words[w], lo, hi);
-                    const uint32_t b0 = prmt(lo, hi, 0x5140);     // nibbles 0,1 of this half
-                    const uint32_t b1 = prmt(lo, hi, 0x7362);     // nibbles 2,3
-                    mma16816<T>(s_acc[nt], qa[2 * w + e][0], 0u, qa[2 * w + e][1], 0u, b0, b1);
-                }
+            for (int c = 0; c < 2; ++c) {
+                const int t1 = acc_h[c] * 256 + (acc_h[c + 2] + acc_l[c]);
+                const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(acc_l[c + 2]));
+                sc[2 * nt + c] = f * (q_factor * (c ? ku.y : ku.x));
+            }
+        }
+        if (n_valid < kTile) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int tok = 8 * (x >> 1) + 2 * tig + (x & 1);
+                if (tok >= n_valid) sc[x] = -INFINITY;
             }
         }
 
         // ---- online softmax for head g over this thread's 4 columns ----
-        float sc[4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int tok = 8 * nt + 2 * tig + c;
-                sc[2 * nt + c] = tok < n_valid ? s_acc[nt][c] * p.qk_scale : -INFINITY;
-            }
         float m_new = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
         m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 1));
         m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 2));
-        m_new = fmaxf(m_new, m_run);
-        // every tile holds at least one valid token, so m_new is finite
-        const bool grew = m_new > m_run;
+        // The running reference m_run only moves when the tile maximum exceeds it by more than 8
+        // (probabilities then stay below 2^8, harmless in fp32), which makes rescaling rare.
+        // Every tile holds at least one valid token, so m_new is finite; m_run starts at -inf.
+        const bool grew = m_new > m_run + 8.0f;
         if (__any_sync(0xffffffffu, grew)) {
-            const float alpha = exp2f(m_run - m_new);      // 0 on the first tile
+            const float m_upd = grew ? m_new : m_run;
+            const float alpha = ex2_approx(m_run - m_upd);      // 0 on the first tile, 1 if unchanged
             l_run *= alpha;
             // accumulator columns are heads 2tig, 2tig+1: fetch their factors from rows g'
             const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * tig) * 4);
@@ -442,12 +595,12 @@ decode_split_kernel(const DecodeParams p) {
                 o_acc[mt][0] *= a0; o_acc[mt][1] *= a1;
                 o_acc[mt][2] *= a0; o_acc[mt][3] *= a1;
             }
-            m_run = m_new;
+            m_run = m_upd;
         }
         float pr[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            pr[c] = exp2f(sc[c] - m_run);
+            pr[c] = ex2_approx(sc[c] - m_run);
             l_run += pr[c];
         }
         // P as mma B operand (k = tokens 2tig,2tig+1 | 2tig+8,2tig+9; n = head g), hi + lo parts
@@ -456,50 +609,33 @@ decode_split_kernel(const DecodeParams p) {
         const uint32_t pl0 = pack_pair<T>(pr[0] - h0.x, pr[1] - h0.y);
         const uint32_t pl1 = pack_pair<T>(pr[2] - h1.x, pr[3] - h1.y);
 
-        // ---- O^T += V^T P^T : rows = this thread's 16 head-dim slots, columns = heads ----
+        // ---- decompress V into the transposition buffer: lane = (token tv, half row) ----
         {
-            const int ta = 2 * tig, tb = 2 * tig + 8;      // token pairs (ta,ta+1) and (tb,tb+1)
-            uint2 vw[4];
-            Table<VB> tv[4];
+            const Table<VB> tb = load_table<VB>(ws.tbl_v[tv]);
+            const uint4 va = *reinterpret_cast<const uint4*>(&st.v[tv][32 * vhalf]);
+            const uint4 vb = *reinterpret_cast<const uint4*>(&st.v[tv][32 * vhalf + 16]);
+            const uint32_t words[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
 #pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const int tok = (x < 2 ? ta : tb) + (x & 1);
-                vw[x] = *reinterpret_cast<const uint2*>(&st.v[tok][8 * g]);
-#pragma unroll
-                for (int r4 = 0; r4 < Table<VB>::kRegs / 4; ++r4) {
-                    const uint4 q4 = *reinterpret_cast<const uint4*>(&ws.tbl_v[tok][4 * r4]);
-                    tv[x].r[4 * r4] = q4.x; tv[x].r[4 * r4 + 1] = q4.y;
-                    tv[x].r[4 * r4 + 2] = q4.z; tv[x].r[4 * r4 + 3] = q4.w;
-                }
-            }
-#pragma unroll
-            for (int sg = 0; sg < 4; ++sg) {               // selector sg covers nibbles 4sg..4sg+3
-                uint32_t pairreg[2][4];                     // [pair a|b][nibble] = (tok, tok+1) halves
-#pragma unroll
-                for (int pb = 0; pb < 2; ++pb) {
-                    uint32_t lo0, hi0, lo1, hi1;
-                    const uint32_t w0 = (sg < 2) ? vw[2 * pb].x : vw[2 * pb].y;
-                    const uint32_t w1 = (sg < 2) ? vw[2 * pb + 1].x : vw[2 * pb + 1].y;
-                    lookup4<VB>(tv[2 * pb], (sg & 1) ? (w0 >> 16) : w0, lo0, hi0);
-                    lookup4<VB>(tv[2 * pb + 1], (sg & 1) ? (w1 >> 16) : w1, lo1, hi1);
-                    const uint32_t pl = prmt(lo0, lo1, 0x5140), pl2 = prmt(lo0, lo1, 0x7362);
-                    const uint32_t ph = prmt(hi0, hi1, 0x5140), ph2 = prmt(hi0, hi1, 0x7362);
-                    pairreg[pb][0] = prmt(pl, ph, 0x5140);
-                    pairreg[pb][1] = prmt(pl, ph, 0x7362);
-                    pairreg[pb][2] = prmt(pl2, ph2, 0x5140);
-                    pairreg[pb][3] = prmt(pl2, ph2, 0x7362);
-                }
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int mt = 2 * sg + half;
-                    const uint32_t a0 = pairreg[0][2 * half], a1 = pairreg[0][2 * half + 1];
-                    const uint32_t a2 = pairreg[1][2 * half], a3 = pairreg[1][2 * half + 1];
-                    mma16816<T>(o_acc[mt], a0, a1, a2, a3, ph0, ph1);
-                    mma16816<T>(o_acc[mt], a0, a1, a2, a3, pl0, pl1);
-                }
+            for (int w = 0; w < 8; ++w) {
+                uint32_t lo0, hi0, lo1, hi1;
+                lookup4<VB>(tb, words[w], lo0, hi0);
+                lookup4<VB>(tb, words[w] >> 16, lo1, hi1);
+                // chunk (8*vhalf + w) ^ (tv & 7): vt rows are 256-byte aligned, so XOR the address
+                st_shared_v4(vt_store_base ^ (16u * w), prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
+                             prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
             }
         }
-        __syncwarp();        // the stage and the tables may be overwritten from here on
+        __syncwarp();
+
+        // ---- O^T += V^T P^T : rows = 16 head-dim positions per m-tile, columns = heads ----
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, lm_base ^ (32u * mt));
+            mma16816<T>(o_acc[mt], a[0], a[1], a[2], a[3], ph0, ph1);
+            mma16816<T>(o_acc[mt], a[0], a[1], a[2], a[3], pl0, pl1);
+        }
+        __syncwarp();        // the stage, the tables and vt may be overwritten from here on
     }
     cp_async_wait<0>();
 
@@ -515,12 +651,13 @@ decode_split_kernel(const DecodeParams p) {
         if (tig == 0) { m_s[g] = m_run; l_s[g] = l_run; }
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
-            // rows g / g+8 of m-tile mt are nibbles 2mt / 2mt+1 = head-dim 16g+2mt+1 / 16g+2mt
-            const int d = 16 * g + 2 * mt;
-            *reinterpret_cast<float2*>(&o_s[(2 * tig) * kHeadDim + d]) =
-                make_float2(o_acc[mt][2], o_acc[mt][0]);
-            *reinterpret_cast<float2*>(&o_s[(2 * tig + 1) * kHeadDim + d]) =
-                make_float2(o_acc[mt][3], o_acc[mt][1]);
+            // row g of m-tile mt is position g of 8-wide chunk 2mt, i.e. head-dim 16mt + (g^1);
+            // row g+8 is the same position of chunk 2mt+1
+            const int d = 16 * mt + (g ^ 1);
+            o_s[(2 * tig) * kHeadDim + d] = o_acc[mt][0];
+            o_s[(2 * tig + 1) * kHeadDim + d] = o_acc[mt][1];
+            o_s[(2 * tig) * kHeadDim + d + 8] = o_acc[mt][2];
+            o_s[(2 * tig + 1) * kHeadDim + d + 8] = o_acc[mt][3];
         }
     }
     __syncthreads();
