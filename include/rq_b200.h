@@ -120,6 +120,30 @@ int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq, int64_t
               const float* rotation, float sm_scale, int max_seq_len, void* workspace,
               size_t workspace_bytes, int num_splits, void* stream);
 
+/*
+ * Fused paged INT8 prefill attention: causal attention of new query tokens over the compressed
+ * cache (which already holds those tokens).  Replaces fused_paged_rq_int8_prefill
+ * (triton/fused_paged_rq_int8_prefill.py:247-363) including its two rotations (:322, :359).
+ * QK^T runs on the tcgen05 INT8 tensor path with one scale per query row and per key, PV on the
+ * tcgen05 16-bit path; both accumulate in tensor memory.
+ *
+ *   q, out         (num_tokens, H_Q, 128) in `dtype` (f16 or bf16); strides in elements
+ *   cu_seqlens_q   int32[num_seqs + 1] device array: sequence s owns query rows
+ *                  [cu[s], cu[s+1]); NULL = one sequence owning all rows (the reference contract)
+ *   seq_lens       int32[num_seqs]: cached tokens per sequence, new tokens included; the query
+ *                  rows of a sequence are its last rows (the reference requires q_len == seq_len)
+ *   max_q_len      upper bound of the per-sequence query length (host value, 0 = num_tokens)
+ *   error_flag     optional device int32, set to 1 if a bounded device-side wait expired
+ */
+int rq_prefill_int8(const void* q, void* out, int dtype, int64_t q_stride_tok,
+                    int64_t q_stride_head, int64_t o_stride_tok, int64_t o_stride_head,
+                    const int32_t* cu_seqlens_q, int num_tokens, int num_seqs, int max_q_len,
+                    int num_q_heads, int num_kv_heads, int head_dim, const uint8_t* kv_cache,
+                    int64_t num_blocks, int block_size, int total_bytes, const int32_t* block_table,
+                    int64_t block_table_stride, const int32_t* seq_lens, const float* centroids_k,
+                    int n_centroids_k, const float* centroids_v, int n_centroids_v,
+                    const float* rotation, float sm_scale, int* error_flag, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

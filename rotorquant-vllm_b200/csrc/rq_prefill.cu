@@ -1,0 +1,639 @@
+// Fused paged INT8 prefill attention over the RotorQuant cache on tcgen05 tensor cores, sm_100a.
+//
+// Replaces fused_paged_rq_int8_prefill (triton/fused_paged_rq_int8_prefill.py:43-363 of the
+// reference: one sequence, 64-row Q tiles, mma.sync-class IMMA through Triton, K dequantised and
+// re-quantised for every Q tile and every query head, no causal tile skipping) and the two dense
+// rotations around it.  This kernel handles several sequences (cu_seqlens_q), a cached prefix
+// (query rows are the last rows of the sequence), stacks the G query heads of a KV head into the
+// MMA M dimension so that a K/V tile is dequantised once per GQA group, and skips KV tiles that
+// are entirely masked.
+//
+// One CTA = 128 MMA rows = (128 / G) query tokens x G heads of one (sequence, KV head); one
+// thread owns one row (= one TMEM lane).  Per 128-key tile:
+//   1. every thread dequantises one key: K -> int8 codes with a per-key scale (8/16-entry code
+//      table, PRMT lookup), V -> exact round_T(centroid * norm) values; both go to shared memory
+//      in the tcgen05 core-matrix layout (no swizzle);
+//   2. S = Q K^T   tcgen05.mma kind::i8, int32 accumulator in TMEM (4 instructions, K = 32 each);
+//   3. each thread reads its row of S from TMEM, scales by q_scale[row] * k_scale[key], applies
+//      the causal mask, runs the online softmax, writes P (bf16/f16) to shared memory;
+//   4. O += P V    tcgen05.mma kind::f16, fp32 accumulator in TMEM (8 instructions, K = 16 each).
+// The epilogue divides by the row sum, rounds, applies R, rounds and stores.
+//
+// INT8 scheme (the reference quantises Q per 64x128 tile and K per BLOCK_N x 128 tile with
+// round-half-up-then-truncate, fused_paged_rq_int8_prefill.py:113-115,:176-178; here the scales
+// are per query row and per key, round to nearest even):
+//   q_i8[m][d] = rint(q_rot[m][d] * 127 / max_d |q_rot[m][d]|),  k_i8[t][d] likewise from the
+//   decompressed key;  score = q_scale[m] * k_scale[t] * sum_d q_i8 k_i8.
+//
+// Every wait on an mbarrier is bounded; on expiry the CTA records an error, frees its TMEM and
+// returns.
+#include "rq_common.cuh"
+
+namespace rq {
+
+constexpr int kPfThreads = 128;
+constexpr int kPfRows = 128;          // MMA M
+constexpr int kPfKeys = 128;          // keys per tile (MMA N of S, K extent of P V)
+constexpr uint32_t kTmemCols = 256;   // S: columns 0..127 (int32), O: columns 128..255 (fp32)
+constexpr long long kWaitCycles = 2000000000LL;   // ~1 s bound on every barrier wait
+
+struct PrefillParams {
+    const void* q;
+    void* out;
+    int64_t q_stride_tok, q_stride_head, o_stride_tok, o_stride_head;
+    const int32_t* cu_seqlens_q;      // nullptr: one sequence owning all rows
+    int num_tokens;
+    int H, Hq, G;
+    int tokens_per_tile;              // 128 / G
+    const uint8_t* cache;
+    int64_t num_blocks;
+    int block_size;
+    int total_bytes;
+    const int32_t* block_table;
+    int64_t bt_stride;
+    const int32_t* seq_lens;
+    const float* cent_k;
+    const float* cent_v;
+    const float* rotation;
+    float qk_scale;                   // sm_scale * log2(e)
+    int* error_flag;                  // optional device int, set non-zero when a wait expired
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+// Wait for the phase with the given parity to complete; false if the bound expired.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    const long long start = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (clock64() - start > kWaitCycles) return false;
+    }
+}
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+// 32 consecutive columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, no swizzle: operands are stored as 8-row x 16-byte core
+// matrices (128 contiguous bytes each).  lbo / sbo are the byte distances between core matrices
+// along the two tile directions as the tcgen05 descriptor defines them for the operand's major.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) |
+           (static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16) |
+           (static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32) |
+           (1ull << 46);          // descriptor version of sm_100
+}
+
+template <typename T> struct PfType;
+template <> struct PfType<__nv_bfloat16> { static constexpr uint32_t kFmt = 1; };
+template <> struct PfType<__half> { static constexpr uint32_t kFmt = 0; };
+
+template <typename T>
+__device__ __forceinline__ uint32_t pf_pack(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pf_pack<__nv_bfloat16>(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+template <>
+__device__ __forceinline__ uint32_t pf_pack<__half>(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+template <typename T>
+__device__ __forceinline__ float2 pf_unpack(uint32_t v);
+template <>
+__device__ __forceinline__ float2 pf_unpack<__nv_bfloat16>(uint32_t v) {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+}
+template <>
+__device__ __forceinline__ float2 pf_unpack<__half>(uint32_t v) {
+    return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+template <typename T>
+__device__ __forceinline__ float pf_round(float v) {
+    return pf_unpack<T>(pf_pack<T>(v, 0.0f)).x;
+}
+__device__ __forceinline__ float pf_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---- shared memory -------------------------------------------------------------------------
+//
+// Operand tiles in core-matrix order (a core matrix = 8 rows x 16 bytes, 128 contiguous bytes):
+//   q, k : int8,  K-major   core index = (row / 8) * 8 + (byte / 16)     row = query row | key
+//   p    : 16-bit, K-major  core index = (row / 8) * 16 + (key / 8)
+//   v    : 16-bit, MN-major core index = (key / 8) * 16 + (dim / 8), core row = key % 8
+// Within a 128-byte K row and within an 8-wide V chunk, position x holds head-dim x ^ 1 (the
+// nibble order of the cache); q is stored the same way and the epilogue undoes it for O.
+struct __align__(128) PrefillSmem {
+    uint8_t q[kPfRows * kHeadDim];
+    uint8_t k[kPfKeys * kHeadDim];
+    uint16_t v[kPfKeys * kHeadDim];
+    uint16_t p[kPfRows * kPfKeys];
+    float k_scale[kPfKeys];
+    float rot[32 * 16];
+    float cb[2][16];
+    uint64_t bar_s, bar_o;
+    uint32_t tmem_base;
+};
+
+// 64 index bytes of one (token, head) from global memory; `align` is 16, 8 or 4.
+__device__ __forceinline__ void load_idx64(const uint8_t* src, int align, uint32_t (&w)[16]) {
+    if (align == 16) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(src) + i);
+            w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
+        }
+    } else if (align == 8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint2 x = __ldg(reinterpret_cast<const uint2*>(src) + i);
+            w[2 * i] = x.x; w[2 * i + 1] = x.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) w[i] = __ldg(reinterpret_cast<const uint32_t*>(src) + i);
+    }
+}
+
+// Four table bytes selected by the four nibbles of sel[15:0]; the table has 8 (BITS 3) or 16
+// (BITS 4) byte entries in 2 or 4 registers.
+template <int BITS>
+__device__ __forceinline__ uint32_t byte_lookup(const uint32_t* tbl, uint32_t sel) {
+    if constexpr (BITS == 3) {
+        return prmt(tbl[0], tbl[1], sel);
+    } else {
+        const uint32_t s7 = sel & 0x7777u;
+        const uint32_t y = prmt(sel, sel << 4, 0x5410);
+        const uint32_t m = prmt(y, y, 0x9B8A);       // byte i = 0xFF when nibble i has its top bit set
+        const uint32_t a = prmt(tbl[0], tbl[1], s7), b = prmt(tbl[2], tbl[3], s7);
+        return (a & ~m) | (b & m);
+    }
+}
+
+template <typename T, int KB, int VB>
+__global__ void __launch_bounds__(kPfThreads)
+prefill_int8_kernel(const PrefillParams p) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    PrefillSmem& sm = *reinterpret_cast<PrefillSmem*>(smem_raw);
+    constexpr int NK = 1 << KB, NV = 1 << VB;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int kvh = blockIdx.y, seq = blockIdx.z;
+    const int q_begin = p.cu_seqlens_q ? __ldg(p.cu_seqlens_q + seq) : 0;
+    const int q_end = p.cu_seqlens_q ? __ldg(p.cu_seqlens_q + seq + 1) : p.num_tokens;
+    const int q_len = max(q_end - q_begin, 0);
+    const int kv_len = max(__ldg(p.seq_lens + seq), 0);
+    const int tiles_m = (q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
+    // heavy (late) query tiles first
+    const int m_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    if (m_tile >= tiles_m || kv_len == 0) {
+        // rows of an empty sequence still get a defined (zero) output
+        if (m_tile < tiles_m) {
+            const int tl = tid / p.G, h = tid % p.G;
+            const int tok = m_tile * p.tokens_per_tile + tl;
+            if (tl < p.tokens_per_tile && tok < q_len) {
+                T* dst = static_cast<T*>(p.out) + (q_begin + tok) * p.o_stride_tok +
+                         static_cast<int64_t>(kvh * p.G + h) * p.o_stride_head;
+                for (int d = 0; d < kHeadDim; d += 8) *reinterpret_cast<uint4*>(dst + d) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        return;
+    }
+
+    // this thread's row: query token and head; absolute position of the token in its sequence
+    const int tok_local = tid / p.G, head_local = tid % p.G;
+    const int tok = m_tile * p.tokens_per_tile + tok_local;
+    const bool row_valid = tok_local < p.tokens_per_tile && tok < q_len;
+    const int pos = row_valid ? kv_len - q_len + tok : -1;
+    const int last_tok = min(q_len, (m_tile + 1) * p.tokens_per_tile) - 1;
+    const int max_pos = kv_len - q_len + last_tok;                  // >= 0 for the CTA
+    const int n_tiles = min(max_pos, kv_len - 1) / kPfKeys + 1;
+
+    // ---- set-up: barriers, TMEM, parameters ----
+    if (tid == 0) {
+        mbar_init(&sm.bar_s, 1);
+        mbar_init(&sm.bar_o, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(&sm.tmem_base, kTmemCols);
+    for (int i = tid; i < 32 * 16; i += kPfThreads) {
+        const int g = i >> 4, j = (i >> 2) & 3, k = i & 3;
+        sm.rot[i] = __ldg(p.rotation + (4 * g + j) * kHeadDim + 4 * g + k);      // R[4g+j][4g+k]
+    }
+    if (tid < 32) {
+        const int kv = tid >> 4, i = tid & 15;
+        const int n = kv ? NV : NK;
+        sm.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(tid) << 16);   // TMEM lane = row
+    const uint32_t core_row_off = (tid >> 3) * 1024 + (tid & 7) * 16;       // q/k tiles: 8 chunks per row group
+
+    // ---- Q: rotate, round, quantise this row to int8 ----
+    float q_scale = 0.0f;
+    {
+        uint32_t packed[64];                    // rotated, rounded row as T pairs (d, d+1)
+        float mx = 0.0f;
+        if (row_valid) {
+            const T* src = static_cast<const T*>(p.q) + (q_begin + tok) * p.q_stride_tok +
+                           static_cast<int64_t>(kvh * p.G + head_local) * p.q_stride_head;
+#pragma unroll
+            for (int b = 0; b < 32; ++b) {
+                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src + 4 * b));
+                const float2 x01 = pf_unpack<T>(raw.x), x23 = pf_unpack<T>(raw.y);
+                float r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 rr = *reinterpret_cast<const float4*>(&sm.rot[b * 16 + j * 4]);
+                    float acc = __fmul_rn(x01.x, rr.x);
+                    acc = __fmaf_rn(x01.y, rr.y, acc);
+                    acc = __fmaf_rn(x23.x, rr.z, acc);
+                    acc = __fmaf_rn(x23.y, rr.w, acc);
+                    r[j] = acc;
+                }
+                packed[2 * b] = pf_pack<T>(r[0], r[1]);
+                packed[2 * b + 1] = pf_pack<T>(r[2], r[3]);
+                const float2 a = pf_unpack<T>(packed[2 * b]), c = pf_unpack<T>(packed[2 * b + 1]);
+                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(c.x), fabsf(c.y))));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) packed[i] = 0u;
+        }
+        const bool ok = mx > 0.0f && mx <= 3.0e38f;
+        const float inv = ok ? __fdiv_rn(127.0f, mx) : 0.0f;
+        q_scale = ok ? __fdiv_rn(mx, 127.0f) : 0.0f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {           // 16 head-dims = 16 bytes per chunk
+            uint32_t wds[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float2 a = pf_unpack<T>(packed[8 * c + 2 * w]), b = pf_unpack<T>(packed[8 * c + 2 * w + 1]);
+                const int i0 = __float2int_rn(a.x * inv), i1 = __float2int_rn(a.y * inv);
+                const int i2 = __float2int_rn(b.x * inv), i3 = __float2int_rn(b.y * inv);
+                // position x holds head-dim x ^ 1
+                wds[w] = (i1 & 0xFF) | ((i0 & 0xFF) << 8) | ((i3 & 0xFF) << 16) | ((i2 & 0xFF) << 24);
+            }
+            *reinterpret_cast<uint4*>(&sm.q[core_row_off + c * 128]) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+        }
+    }
+    const float row_factor = q_scale * p.qk_scale;
+
+    // descriptors and instruction words
+    const uint32_t idesc_s = (2u << 4) | (1u << 7) | (1u << 10) | ((kPfKeys >> 3) << 17) | ((kPfRows >> 4) << 24);
+    const uint32_t idesc_o = (1u << 4) | (PfType<T>::kFmt << 7) | (PfType<T>::kFmt << 10) | (1u << 16) |
+                             ((kHeadDim >> 3) << 17) | ((kPfRows >> 4) << 24);
+    const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p);
+
+    const SlotLayout lay = slot_layout(p.H);
+    const int v_align = (lay.v_idx % 16 == 0) ? 16 : ((lay.v_idx % 8 == 0) ? 8 : 4);
+    const int32_t* bt_row = p.block_table + seq * p.bt_stride;
+
+    float m_run = -INFINITY, l_run = 0.0f;
+    uint32_t phase = 0;
+    bool failed = false;
+
+#pragma unroll 1
+    for (int j = 0; j < n_tiles; ++j) {
+        // ---- 1. dequantise key j*128 + tid: K codes + scale, V values ----
+        {
+            const int kt = j * kPfKeys + tid;
+            const bool valid = kt < kv_len;
+            uint32_t kw[16], vw[16];
+            float norm_k = 0.0f, norm_v = 0.0f;
+            if (valid) {
+                int64_t blk = __ldg(bt_row + kt / p.block_size);
+                blk = blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
+                const uint8_t* slot = p.cache + (blk * p.block_size + kt % p.block_size) * p.total_bytes;
+                load_idx64(slot + lay.k_idx + kvh * kHalfDim, 16, kw);
+                load_idx64(slot + lay.v_idx + kvh * kHalfDim, v_align, vw);
+                norm_k = __ldg(reinterpret_cast<const float*>(slot + lay.k_norm) + kvh);
+                norm_v = __ldg(reinterpret_cast<const float*>(slot + lay.v_norm) + kvh);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { kw[i] = 0u; vw[i] = 0u; }
+            }
+            // K: int8 code table of this key
+            float tv[NK];
+            float mx = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NK; ++i) {
+                tv[i] = pf_round<T>(__fmul_rn(sm.cb[0][i], norm_k));
+                mx = fmaxf(mx, fabsf(tv[i]));
+            }
+            const bool ok = mx > 0.0f && mx <= 3.0e38f;
+            const float inv = ok ? __fdiv_rn(127.0f, mx) : 0.0f;
+            sm.k_scale[tid] = ok ? __fdiv_rn(mx, 127.0f) : 0.0f;
+            uint32_t ktbl[NK / 4];
+#pragma unroll
+            for (int i = 0; i < NK / 4; ++i) {
+                const int c0 = __float2int_rn(tv[4 * i] * inv), c1 = __float2int_rn(tv[4 * i + 1] * inv);
+                const int c2 = __float2int_rn(tv[4 * i + 2] * inv), c3 = __float2int_rn(tv[4 * i + 3] * inv);
+                ktbl[i] = (c0 & 0xFF) | ((c1 & 0xFF) << 8) | ((c2 & 0xFF) << 16) | ((c3 & 0xFF) << 24);
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t a = kw[2 * c], b = kw[2 * c + 1];
+                *reinterpret_cast<uint4*>(&sm.k[core_row_off + c * 128]) =
+                    make_uint4(byte_lookup<KB>(ktbl, a), byte_lookup<KB>(ktbl, a >> 16),
+                               byte_lookup<KB>(ktbl, b), byte_lookup<KB>(ktbl, b >> 16));
+            }
+            // V: exact decompressed values, low- and high-byte planes of the T bit patterns
+            uint32_t vlo[NV / 4], vhi[NV / 4];
+#pragma unroll
+            for (int i = 0; i < NV / 4; ++i) {
+                const uint32_t p01 = pf_pack<T>(__fmul_rn(sm.cb[1][4 * i], norm_v), __fmul_rn(sm.cb[1][4 * i + 1], norm_v));
+                const uint32_t p23 = pf_pack<T>(__fmul_rn(sm.cb[1][4 * i + 2], norm_v), __fmul_rn(sm.cb[1][4 * i + 3], norm_v));
+                vlo[i] = prmt(p01, p23, 0x6420);
+                vhi[i] = prmt(p01, p23, 0x7531);
+            }
+            uint8_t* vdst = reinterpret_cast<uint8_t*>(sm.v) + (tid >> 3) * (16 * 128) + (tid & 7) * 16;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {       // 8 head-dims = one 32-bit index word per chunk
+                const uint32_t lo0 = byte_lookup<VB>(vlo, vw[c]), hi0 = byte_lookup<VB>(vhi, vw[c]);
+                const uint32_t lo1 = byte_lookup<VB>(vlo, vw[c] >> 16), hi1 = byte_lookup<VB>(vhi, vw[c] >> 16);
+                *reinterpret_cast<uint4*>(vdst + c * 128) =
+                    make_uint4(prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
+                               prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
+            }
+        }
+        fence_async_proxy();
+        tc_fence_before();
+        __syncthreads();
+
+        // ---- 2. S = Q K^T ----
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                tc_mma_i8(tmem, smem_desc(q_addr + 256 * s, 128, 1024), smem_desc(k_addr + 256 * s, 128, 1024),
+                          idesc_s, s > 0 ? 1u : 0u);
+            tc_commit(&sm.bar_s);
+        }
+        if (__syncthreads_or(!mbar_wait(&sm.bar_s, phase))) { failed = true; break; }   // uniform exit
+        tc_fence_after();
+
+        // ---- 3. online softmax on this thread's row; P -> shared memory ----
+        const int key0 = j * kPfKeys;
+        float m_tile = -INFINITY;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + 32 * ch, r);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float s = static_cast<float>(static_cast<int>(r[c])) * (row_factor * sm.k_scale[32 * ch + c]);
+                if (key0 + 32 * ch + c <= pos) m_tile = fmaxf(m_tile, s);
+            }
+        }
+        const float m_new = fmaxf(m_run, m_tile);
+        const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+        const float alpha = (m_new == m_run) ? 1.0f : ((m_run == -INFINITY) ? 0.0f : pf_ex2(m_run - m_use));
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t r[32];
+                tmem_ld32(lane_addr + kPfKeys + 32 * ch, r);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+                tmem_st32(lane_addr + kPfKeys + 32 * ch, r);
+            }
+        }
+        l_run *= alpha;
+        m_run = m_new;
+        uint8_t* prow = reinterpret_cast<uint8_t*>(sm.p) + (tid >> 3) * (16 * 128) + (tid & 7) * 16;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + 32 * ch, r);
+            uint32_t pk[16];
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                const float s0 = static_cast<float>(static_cast<int>(r[c])) * (row_factor * sm.k_scale[32 * ch + c]);
+                const float s1 = static_cast<float>(static_cast<int>(r[c + 1])) * (row_factor * sm.k_scale[32 * ch + c + 1]);
+                const float p0 = (key0 + 32 * ch + c <= pos) ? pf_ex2(s0 - m_use) : 0.0f;
+                const float p1 = (key0 + 32 * ch + c + 1 <= pos) ? pf_ex2(s1 - m_use) : 0.0f;
+                pk[c >> 1] = pf_pack<T>(p0, p1);
+                const float2 back = pf_unpack<T>(pk[c >> 1]);     // the row sum uses what the MMA sees
+                l_run += back.x + back.y;
+            }
+#pragma unroll
+            for (int kc = 0; kc < 4; ++kc)
+                *reinterpret_cast<uint4*>(prow + (4 * ch + kc) * 128) =
+                    make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
+        }
+        fence_async_proxy();
+        tc_fence_before();
+        __syncthreads();
+
+        // ---- 4. O += P V ----
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                tc_mma_f16(tmem + kPfKeys, smem_desc(p_addr + 256 * s, 128, 2048),
+                           smem_desc(v_addr + 4096 * s, 2048, 128), idesc_o, (j > 0 || s > 0) ? 1u : 0u);
+            tc_commit(&sm.bar_o);
+        }
+        if (__syncthreads_or(!mbar_wait(&sm.bar_o, phase))) { failed = true; break; }
+        tc_fence_after();
+        phase ^= 1u;
+    }
+
+    // ---- epilogue: O / l, round, rotate by R, round, store ----
+    if (!failed) {
+        const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        T* dst = row_valid ? static_cast<T*>(p.out) + (q_begin + tok) * p.o_stride_tok +
+                                 static_cast<int64_t>(kvh * p.G + head_local) * p.o_stride_head
+                           : nullptr;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + kPfKeys + 32 * ch, r);
+            uint32_t outw[16];
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {       // rotation block = head-dims 32ch + 4b .. + 3
+                float o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)    // column x of O holds head-dim x ^ 1
+                    o[e] = pf_round<T>(__uint_as_float(r[(4 * b + e) ^ 1]) * inv_l);
+                const float* rb = &sm.rot[(8 * ch + b) * 16];      // rb[k*4 + jj] = R[4g+k][4g+jj]
+                float y[4];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    float acc = __fmul_rn(o[0], rb[jj]);
+                    acc = __fmaf_rn(o[1], rb[4 + jj], acc);
+                    acc = __fmaf_rn(o[2], rb[8 + jj], acc);
+                    acc = __fmaf_rn(o[3], rb[12 + jj], acc);
+                    y[jj] = acc;
+                }
+                outw[2 * b] = pf_pack<T>(y[0], y[1]);
+                outw[2 * b + 1] = pf_pack<T>(y[2], y[3]);
+            }
+            if (dst != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    *reinterpret_cast<uint4*>(dst + 32 * ch + 8 * i) =
+                        make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
+            }
+        }
+    } else if (tid == 0 && p.error_flag != nullptr) {
+        atomicExch(p.error_flag, 1);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+template <typename T, int KB, int VB>
+static int launch_prefill(const PrefillParams& p, int m_tiles, int num_seqs, cudaStream_t st) {
+    const size_t smem = sizeof(PrefillSmem);
+    if (int e = ensure_smem(prefill_int8_kernel<T, KB, VB>, smem)) return e;
+    dim3 grid(m_tiles, p.H, num_seqs);
+    prefill_int8_kernel<T, KB, VB><<<grid, kPfThreads, smem, st>>>(p);
+    return check_cuda(cudaGetLastError(), "rq_prefill_int8 launch");
+}
+
+template <typename T>
+static int dispatch_prefill(const PrefillParams& p, int m_tiles, int num_seqs, int kb, int vb, cudaStream_t st) {
+    if (kb == 3 && vb == 3) return launch_prefill<T, 3, 3>(p, m_tiles, num_seqs, st);
+    if (kb == 4 && vb == 3) return launch_prefill<T, 4, 3>(p, m_tiles, num_seqs, st);
+    if (kb == 3 && vb == 4) return launch_prefill<T, 3, 4>(p, m_tiles, num_seqs, st);
+    return launch_prefill<T, 4, 4>(p, m_tiles, num_seqs, st);
+}
+
+}  // namespace rq
+
+using namespace rq;
+
+extern "C" int rq_prefill_int8(const void* q, void* out, int dtype, int64_t q_stride_tok,
+                               int64_t q_stride_head, int64_t o_stride_tok, int64_t o_stride_head,
+                               const int32_t* cu_seqlens_q, int num_tokens, int num_seqs,
+                               int max_q_len, int num_q_heads, int num_kv_heads, int head_dim,
+                               const uint8_t* kv_cache, int64_t num_blocks, int block_size,
+                               int total_bytes, const int32_t* block_table,
+                               int64_t block_table_stride, const int32_t* seq_lens,
+                               const float* centroids_k, int n_centroids_k,
+                               const float* centroids_v, int n_centroids_v, const float* rotation,
+                               float sm_scale, int* error_flag, void* stream) {
+    if (num_tokens < 0 || num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_blocks < 0 ||
+        block_size <= 0 || max_q_len < 0)
+        return fail(RQ_ERR_INVALID_ARG, "rq_prefill_int8: negative or zero size");
+    if (head_dim != kHeadDim)
+        return fail(RQ_ERR_UNSUPPORTED, "rq_prefill_int8: head_dim %d (only 128)", head_dim);
+    if (dtype != RQ_DTYPE_F16 && dtype != RQ_DTYPE_BF16)
+        return fail(RQ_ERR_UNSUPPORTED, "rq_prefill_int8: query dtype must be f16 or bf16");
+    if (num_q_heads % num_kv_heads != 0)
+        return fail(RQ_ERR_INVALID_ARG, "rq_prefill_int8: %d query heads not a multiple of %d KV heads",
+                    num_q_heads, num_kv_heads);
+    const int G = num_q_heads / num_kv_heads;
+    if (G > kPfRows)
+        return fail(RQ_ERR_UNSUPPORTED, "rq_prefill_int8: %d query heads per KV head (at most 128)", G);
+    if (total_bytes != num_kv_heads * kSlotPerHead)
+        return fail(RQ_ERR_INVALID_ARG, "rq_prefill_int8: total_bytes %d != %d heads * 256", total_bytes,
+                    num_kv_heads);
+    if ((n_centroids_k != 8 && n_centroids_k != 16) || (n_centroids_v != 8 && n_centroids_v != 16))
+        return fail(RQ_ERR_UNSUPPORTED, "rq_prefill_int8: codebooks must have 8 or 16 centroids");
+    if (cu_seqlens_q == nullptr && num_seqs != 1)
+        return fail(RQ_ERR_INVALID_ARG, "rq_prefill_int8: %d sequences need cu_seqlens_q", num_seqs);
+    if (num_tokens == 0 || num_seqs == 0) return RQ_OK;
+    if (num_seqs > 65535 || num_kv_heads > 65535)
+        return fail(RQ_ERR_UNSUPPORTED, "rq_prefill_int8: too many sequences or heads for one launch");
+    if (!q || !out || !kv_cache || !block_table || !seq_lens || !centroids_k || !centroids_v || !rotation)
+        return fail(RQ_ERR_INVALID_ARG, "rq_prefill_int8: null pointer");
+    if (!aligned(q, 8) || (q_stride_tok * 2) % 8 != 0 || (q_stride_head * 2) % 8 != 0)
+        return fail(RQ_ERR_ALIGNMENT, "rq_prefill_int8: query rows must be 8-byte aligned");
+    if (!aligned(out, 16) || (o_stride_tok * 2) % 16 != 0 || (o_stride_head * 2) % 16 != 0)
+        return fail(RQ_ERR_ALIGNMENT, "rq_prefill_int8: output rows must be 16-byte aligned");
+    if (!aligned(kv_cache, 16) || !aligned(rotation, 16))
+        return fail(RQ_ERR_ALIGNMENT, "rq_prefill_int8: kv_cache and rotation must be 16-byte aligned");
+
+    PrefillParams p{};
+    p.q = q; p.out = out;
+    p.q_stride_tok = q_stride_tok; p.q_stride_head = q_stride_head;
+    p.o_stride_tok = o_stride_tok; p.o_stride_head = o_stride_head;
+    p.cu_seqlens_q = cu_seqlens_q; p.num_tokens = num_tokens;
+    p.H = num_kv_heads; p.Hq = num_q_heads; p.G = G;
+    p.tokens_per_tile = kPfRows / G;
+    p.cache = kv_cache; p.num_blocks = num_blocks; p.block_size = block_size;
+    p.total_bytes = total_bytes; p.block_table = block_table; p.bt_stride = block_table_stride;
+    p.seq_lens = seq_lens; p.cent_k = centroids_k; p.cent_v = centroids_v; p.rotation = rotation;
+    p.qk_scale = sm_scale * 1.4426950408889634f;
+    p.error_flag = error_flag;
+    const int longest = (max_q_len > 0 && max_q_len < num_tokens) ? max_q_len : num_tokens;
+    const int m_tiles = (longest + p.tokens_per_tile - 1) / p.tokens_per_tile;
+    const int kb = n_centroids_k == 8 ? 3 : 4, vb = n_centroids_v == 8 ? 3 : 4;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == RQ_DTYPE_BF16) return dispatch_prefill<__nv_bfloat16>(p, m_tiles, num_seqs, kb, vb, st);
+    return dispatch_prefill<__half>(p, m_tiles, num_seqs, kb, vb, st);
+}

@@ -33,14 +33,11 @@ _SIGNATURES = {
     "rq_decode_workspace_bytes": (_Z, [_I, _I, _I, _I, _I, _I]),
     "rq_decode": (_I, [_P, _P, _I, _L, _L, _L, _L, _I, _I, _I, _I, _P, _L, _I, _I, _P, _L, _P, _P,
                        _I, _P, _I, _P, _F, _I, _P, _Z, _I, _P]),
+    "rq_prefill_int8": (_I, [_P, _P, _I, _L, _L, _L, _L, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P,
+                             _L, _P, _P, _I, _P, _I, _P, _F, _P, _P]),
 }
 
-# Entry points that newer builds of the library add; bound when present.
-_OPTIONAL = {
-    "rq_prefill_int8_workspace_bytes": (_Z, [_I, _I, _I, _I]),
-    "rq_prefill_int8": (_I, [_P, _P, _I, _L, _L, _L, _L, _P, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P,
-                             _L, _P, _P, _I, _P, _I, _P, _F, _P, _Z, _P]),
-}
+_OPTIONAL: dict = {}
 
 
 def library_path() -> str:

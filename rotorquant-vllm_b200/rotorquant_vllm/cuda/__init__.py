@@ -4,6 +4,7 @@
 from .compress import compress_and_store, iso_compress, planar_compress
 from .decode import decode_workspace_bytes, fused_paged_rq_decode
 from .decompress import iso_decompress, planar_decompress
+from .prefill import fused_paged_rq_int8_prefill
 from .rotation import validate_rotation
 
 __all__ = [
@@ -13,6 +14,7 @@ __all__ = [
     "planar_decompress",
     "compress_and_store",
     "fused_paged_rq_decode",
+    "fused_paged_rq_int8_prefill",
     "decode_workspace_bytes",
     "validate_rotation",
 ]

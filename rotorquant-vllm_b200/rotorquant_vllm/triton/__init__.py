@@ -4,16 +4,12 @@ launchers in ``rotorquant_vllm.cuda``."""
 
 from rotorquant_vllm.cuda import (
     fused_paged_rq_decode,
+    fused_paged_rq_int8_prefill,
     iso_compress,
     iso_decompress,
     planar_compress,
     planar_decompress,
 )
-
-try:  # present once the INT8 prefill kernel is built into the library
-    from rotorquant_vllm.cuda.prefill import fused_paged_rq_int8_prefill
-except ImportError:  # pragma: no cover
-    fused_paged_rq_int8_prefill = None
 
 __all__ = [
     "iso_compress",
