@@ -121,6 +121,38 @@ int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq, int64_t
               size_t workspace_bytes, int num_splits, void* stream);
 
 /*
+ * rq_decode for callers that cannot supply a workspace.  It has no counterpart in the reference.
+ *
+ * Who needs it: a caller that is unable to obtain device memory of its own when the decode call
+ * is made -- for example a serving process that handed all free HBM to its KV-cache pool at
+ * start-up and may not allocate afterwards, or a host runtime that bans allocator calls on its
+ * request path.  The scratch lives in a fixed area of RQ_DECODE_STATIC_SCRATCH_BYTES bytes inside
+ * the library image; every GPU that loads the library holds that area until the process exits.
+ * The function calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * Arguments and results are those of rq_decode without `workspace` / `workspace_bytes`.
+ *   - A call whose splits need more than RQ_DECODE_STATIC_SCRATCH_BYTES (see
+ *     rq_decode_workspace_bytes) is rejected with RQ_ERR_WORKSPACE; nothing is launched.
+ *   - The first call on each device looks up the device address of the area
+ *     (cudaGetSymbolAddress, with that device current).  Make that first call before any stream
+ *     capture on the device.
+ *   - All calls on a device share the one area, which keeps the previous call's contents.  The
+ *     kernels write every scratch entry before they read it, so nothing needs clearing, but two
+ *     calls that overlap on the GPU (different streams) race on it: keep them on one stream or
+ *     order them yourself.
+ */
+#define RQ_DECODE_STATIC_SCRATCH_BYTES (4u << 20)
+int rq_decode_static_scratch(const void* q, void* out, int dtype, int64_t q_stride_seq,
+                             int64_t q_stride_head, int64_t o_stride_seq, int64_t o_stride_head,
+                             int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                             const uint8_t* kv_cache, int64_t num_blocks, int block_size,
+                             int total_bytes, const int32_t* block_table,
+                             int64_t block_table_stride, const int32_t* seq_lens,
+                             const float* centroids_k, int n_centroids_k,
+                             const float* centroids_v, int n_centroids_v, const float* rotation,
+                             float sm_scale, int max_seq_len, int num_splits, void* stream);
+
+/*
  * Fused paged INT8 prefill attention: causal attention of new query tokens over the compressed
  * cache (which already holds those tokens).  Replaces fused_paged_rq_int8_prefill
  * (triton/fused_paged_rq_int8_prefill.py:247-363) including its two rotations (:322, :359).

@@ -20,6 +20,8 @@
 // mma.sync m16n8k16 is used on purpose: M is the 4..8 query heads of one KV head, far below the
 // 128-row tiles tcgen05 needs, and the kernel is bound by HBM bytes and dequantisation
 // instructions, not by tensor throughput.
+#include <mutex>
+
 #include "rq_common.cuh"
 
 namespace rq {
@@ -853,4 +855,63 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == RQ_DTYPE_BF16) return dispatch_bits<__nv_bfloat16>(p, num_seqs, kb, vb, st);
     return dispatch_bits<__half>(p, num_seqs, kb, vb, st);
+}
+
+// ---- decode with library-owned scratch ------------------------------------------------------
+//
+// Some callers have no way to hand rq_decode a workspace: a serving process that gave all free
+// HBM to its KV-cache pool at start-up and must not allocate afterwards, or a host runtime whose
+// request path is forbidden to call an allocator.  For them the library keeps one fixed scratch
+// area per GPU in its own image.  It exists on every GPU that loads the library, for the life
+// of the process, whether or not this entry point is ever called.
+static __device__ __align__(256) unsigned char g_decode_scratch[RQ_DECODE_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_decode_scratch on the current device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use, so the address is looked up
+// once per device with cudaGetSymbolAddress (with that device current) and remembered.
+int static_scratch_address(void** out) {
+    static std::mutex mu;
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    if (int e = rq::check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return e;
+    if (dev < 0 || dev >= 64)
+        return rq::fail(RQ_ERR_UNSUPPORTED, "rq_decode_static_scratch: device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (int e = rq::check_cuda(cudaGetSymbolAddress(&ptr, g_decode_scratch),
+                                   "cudaGetSymbolAddress(decode scratch)"))
+            return e;
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return RQ_OK;
+}
+}  // namespace
+
+extern "C" int rq_decode_static_scratch(const void* q, void* out, int dtype, int64_t q_stride_seq,
+                                        int64_t q_stride_head, int64_t o_stride_seq,
+                                        int64_t o_stride_head, int num_seqs, int num_q_heads,
+                                        int num_kv_heads, int head_dim, const uint8_t* kv_cache,
+                                        int64_t num_blocks, int block_size, int total_bytes,
+                                        const int32_t* block_table, int64_t block_table_stride,
+                                        const int32_t* seq_lens, const float* centroids_k,
+                                        int n_centroids_k, const float* centroids_v,
+                                        int n_centroids_v, const float* rotation, float sm_scale,
+                                        int max_seq_len, int num_splits, void* stream) {
+    const size_t need = rq_decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                                  max_seq_len, num_splits);
+    if (need > static_cast<size_t>(RQ_DECODE_STATIC_SCRATCH_BYTES))
+        return rq::fail(RQ_ERR_WORKSPACE,
+                        "rq_decode_static_scratch: this call needs %zu scratch bytes, the built-in area "
+                        "holds %zu; use rq_decode with a caller-provided workspace",
+                        need, static_cast<size_t>(RQ_DECODE_STATIC_SCRATCH_BYTES));
+    void* scratch = nullptr;
+    if (int e = static_scratch_address(&scratch)) return e;
+    return rq_decode(q, out, dtype, q_stride_seq, q_stride_head, o_stride_seq, o_stride_head, num_seqs,
+                     num_q_heads, num_kv_heads, head_dim, kv_cache, num_blocks, block_size, total_bytes,
+                     block_table, block_table_stride, seq_lens, centroids_k, n_centroids_k, centroids_v,
+                     n_centroids_v, rotation, sm_scale, max_seq_len, scratch,
+                     static_cast<size_t>(RQ_DECODE_STATIC_SCRATCH_BYTES), num_splits, stream);
 }

@@ -33,6 +33,8 @@ _SIGNATURES = {
     "rq_decode_workspace_bytes": (_Z, [_I, _I, _I, _I, _I, _I]),
     "rq_decode": (_I, [_P, _P, _I, _L, _L, _L, _L, _I, _I, _I, _I, _P, _L, _I, _I, _P, _L, _P, _P,
                        _I, _P, _I, _P, _F, _I, _P, _Z, _I, _P]),
+    "rq_decode_static_scratch": (_I, [_P, _P, _I, _L, _L, _L, _L, _I, _I, _I, _I, _P, _L, _I, _I, _P, _L, _P,
+                                      _P, _I, _P, _I, _P, _F, _I, _I, _P]),
     "rq_prefill_int8": (_I, [_P, _P, _I, _L, _L, _L, _L, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P,
                              _L, _P, _P, _I, _P, _I, _P, _F, _P, _P]),
 }
