@@ -34,6 +34,7 @@ for _p in (REPO, os.path.join(REPO, "rotorquant-vllm_b200")):
 
 import torch  # noqa: E402
 
+from rotorquant_vllm import parallel  # noqa: E402
 from rotorquant_vllm import synthetic as syn  # noqa: E402
 from rotorquant_vllm.quantization import IsoQuantMSE, PlanarQuantMSE  # noqa: E402
 from rotorquant_vllm.vllm.rotation import build_rotation_matrix  # noqa: E402
@@ -49,11 +50,13 @@ NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 155.9e6 / 143.2e6
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode_llama8b",
-                    choices=["decode_llama8b", "decode_qwen7b_planar", "decode_70b_long"])
+                    choices=["decode_llama8b", "decode_qwen7b_planar", "decode_70b_long", "prefill_int8"])
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the workload's number of sequences (small cases for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     return ap.parse_args()
@@ -93,59 +96,77 @@ def decode_algorithmic_bytes(seq_lens, num_kv_heads: int, num_q_heads: int, bloc
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while a region runs (read-only
+    NVML queries from a thread every few milliseconds; nvidia-smi as a fallback)."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+               "sw_power_cap": 0x4}
 
     def __init__(self, index: int):
         self.index = index
-        self.proc = None
-        self.lines: list[str] = []
-        self.thread = None
+        self.sm: list[float] = []
+        self.bits = 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        self._handle = None
+
+    def _visible_index(self) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            try:
+                return int(vis.split(",")[self.index])
+            except (ValueError, IndexError):
+                pass
+        return self.index
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
-            return
-        self.thread = threading.Thread(target=self._pump, daemon=True)
-        self.thread.start()
+            import pynvml
 
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self._visible_index())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nvml = None
+        self._thread = threading.Thread(target=self._poll, daemon=True)
+        self._thread.start()
+
+    def _sample(self):
+        if self._nvml is not None:
+            n = self._nvml
+            self.sm.append(float(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM)))
+            try:
+                self.bits |= int(n.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+            except Exception:
+                self.bits |= int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+        else:
+            out = subprocess.run(
+                ["nvidia-smi", "-i", str(self._visible_index()),
+                 "--query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.active",
+                 "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+            parts = [x.strip() for x in out.split(",")]
+            self.sm.append(float(parts[0]))
+            self.max_mhz = float(parts[1])
+            self.bits |= int(parts[2], 16)
+
+    def _poll(self):
+        while not self._stop.is_set():
+            try:
+                self._sample()
+            except Exception:
+                pass
+            self._stop.wait(0.004)
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+        reasons = sorted(name for name, bit in self.REASONS.items() if self.bits & bit)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.sm)}
 
 
 # --------------------------------------------------------------------------------------------
@@ -231,7 +252,8 @@ def run_reference_arm(args, w: syn.Workload) -> None:
     }))
 
 
-def workload_config(w: syn.Workload, world: int, seqs_per_rank: int, sharding: str = "by sequence") -> dict:
+def workload_config(w: syn.Workload, world: int, seqs_per_rank: int, sharding: str = "by sequence",
+                    step: str = "compress-on-write of one new token per sequence + fused paged decode") -> dict:
     return {
         "workload": w.name, "num_seqs": seqs_per_rank * (world if sharding == "by sequence" else 1),
         "context": w.ctx_max if w.ctx_min == w.ctx_max else f"{w.ctx_min}-{w.ctx_max}",
@@ -239,7 +261,7 @@ def workload_config(w: syn.Workload, world: int, seqs_per_rank: int, sharding: s
         "block_size": w.block_size,
         "rq": f"{w.rq_mode}-{w.iso_mode if w.rq_mode == 'iso' else 'givens'} k{w.k_bits} v{w.v_bits}",
         "sharding": sharding,
-        "step": "compress-on-write of one new token per sequence + fused paged decode",
+        "step": step,
         "l2": "compressed cache per GPU is larger than the 126 MB L2",
     }
 
@@ -306,7 +328,7 @@ class GpuJob:
         self.max_seq_len = int(self.seq_lens_host.max())
         self.gathered = None
         if self.sharding == "by KV head" and world > 1:
-            self.gathered = torch.empty(world, B, self.HQ, w.head_dim, dtype=w.dtype, device=device)
+            self.gathered = torch.empty(B, w.num_q_heads, w.head_dim, dtype=w.dtype, device=device)
         torch.cuda.synchronize(device)
 
     # one step on device-resident inputs: 3 kernel launches (compress+store, decode split, merge)
@@ -324,7 +346,7 @@ class GpuJob:
 
     def gather_heads(self):
         if self.gathered is not None:
-            torch.distributed.all_gather_into_tensor(self.gathered, self.out)
+            self.gathered = parallel.gather_head_outputs(self.out)
 
     def algorithmic_bytes(self) -> int:
         return decode_algorithmic_bytes(self.seq_lens_host.tolist(), self.H, self.HQ, self.w.block_size)
@@ -458,9 +480,137 @@ def run_gpu_arm(args, w: syn.Workload) -> None:
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------
+# Prefill workload (secondary metric): compress-on-write of all prompt tokens + INT8 prefill
+# --------------------------------------------------------------------------------------------
+
+PREFILL_STEP = "compress-on-write of all prompt tokens + causal INT8 prefill attention over the cache"
+
+
+def run_prefill_arm(args, w: syn.Workload) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    T, B, H, HQ, D, bs = w.ctx_max, w.batch, w.num_kv_heads, w.num_q_heads, w.head_dim, w.block_size
+    ops = 4 * D * B * HQ * T * (T + 1) // 2          # causal, QK^T + PV, 2 per multiply-add
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        from oracle import rq_oracle
+
+        kq, vq, R = make_quantizers(w)
+        seq_lens = torch.tensor([T], dtype=torch.int32)
+        bt, nb = syn.make_block_table(seq_lens, bs, 0)
+        slots = syn.slot_mapping_for(bt, seq_lens, bs)
+        key, value = syn.make_kv(T, H, D, w.dtype, 0)
+        q = syn.make_queries(T, HQ, D, w.dtype, 0)
+        cache = torch.zeros(nb, bs, H * 256, dtype=torch.uint8)
+
+        def step():
+            rq_oracle.compress_and_store(key, value, cache, slots, R, kq.boundaries, vq.boundaries)
+            return rq_oracle.prefill(q, cache, bt, seq_lens, kq.centroids, vq.centroids, R, H, D, bs)
+
+        steps = max(1, min(args.steps, 5))
+        step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        per = (time.perf_counter() - t0) / steps
+        base = {"value": T / per, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                "sample": f"1 of {B} sequences of {T} tokens, compress + decompress + causal SDPA"}
+        print(json.dumps({"impl": "reference", "metric": "int8_prefill_tokens_per_s", "value": T / per,
+                          "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": 1,
+                          "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                          "config": workload_config(w, 1, B, step=PREFILL_STEP), "cpu_baseline": base, "gpu_launches": 0,
+                          "e2e": {"value": T / per, "unit": UNIT, "h2d_bytes_per_step": 0,
+                                  "d2h_bytes_per_step": 0}}))
+        return
+
+    from rotorquant_vllm import cuda as rq
+
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=device)
+    kq, vq, R = make_quantizers(w)
+    R = R.to(device)
+    kc, vc, kb, vb = (t.to(device) for t in (kq.centroids, vq.centroids, kq.boundaries, vq.boundaries))
+    gen = torch.Generator(device=device).manual_seed(rank)
+    nblk = B * T // bs
+    cache = torch.zeros(nblk, bs, H * 256, dtype=torch.uint8, device=device)
+    bt = torch.randperm(nblk, device=device, generator=gen).to(torch.int32).reshape(B, T // bs).contiguous()
+    pos = torch.arange(T, device=device)
+    slots = torch.cat([bt[s].long()[pos // bs] * bs + pos % bs for s in range(B)])
+    key = torch.randn(B * T, H, D, device=device, generator=gen)
+    value = torch.randn(B * T, H, D, device=device, generator=gen)
+    key[..., 3] *= 10
+    value[..., 3] *= 10
+    key, value = key.to(w.dtype), value.to(w.dtype)
+    q = torch.randn(B * T, HQ, D, device=device, generator=gen).to(w.dtype)
+    sl = torch.full((B,), T, dtype=torch.int32, device=device)
+    cu = (torch.arange(B + 1, device=device) * T).to(torch.int32)
+    out = torch.empty_like(q)
+    flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def attn():
+        rq.fused_paged_rq_int8_prefill(q, cache, bt, sl, kc, vc, R, H, D, bs, out=out, cu_seqlens_q=cu,
+                                       max_q_len=T, error_flag=flag)
+
+    def step():
+        rq.compress_and_store(key, value, cache, slots, R, kb, vb)
+        attn()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if world > 1:
+        torch.distributed.barrier()
+    if sampler:
+        sampler.start()
+    ms = timed(step, args.steps, device) / args.steps
+    attn_ms = timed(attn, args.steps, device) / args.steps
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([ms, attn_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms, attn_ms = t.tolist()
+    if int(flag.item()) != 0:
+        raise SystemExit("bench.py: a bounded device-side wait expired in the prefill kernel")
+    if rank == 0:
+        bf16, kind = 1649.1, "fallback"
+        try:
+            with open(os.path.join(REPO, "MEASURED_PEAKS.json")) as f:
+                bf16, kind = float(json.load(f)["bf16_tflops"]), "measured"
+        except (OSError, KeyError, ValueError):
+            pass
+        peak = 2.0 * bf16           # INT8 dense peak is not measured on this pool: 2 x the bf16 burst figure
+        achieved = ops / (attn_ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "int8_prefill_tokens_per_s", "value": world * B * T / (ms * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8/bf16",
+            "data": "synthetic", "config": workload_config(w, world, B, step=PREFILL_STEP), "clocks": clocks,
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "prefill_int8_kernel", "achieved": achieved,
+                         "peak": peak, "peak_kind": f"2 x {kind} bf16 burst (INT8 peak assumed)",
+                         "unit": "TOP/s", "frac": achieved / peak, "kernel_ms": attn_ms,
+                         "algorithmic_ops": ops, "traffic": None},
+        }))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
 def main():
     args = parse_args()
     w = syn.WORKLOADS[args.workload]
+    if args.batch > 0:
+        import dataclasses
+
+        w = dataclasses.replace(w, batch=args.batch)
+    if args.workload == "prefill_int8":
+        run_prefill_arm(args, w)
+        return
     if args.impl == "reference":
         run_reference_arm(args, w)
     else:
