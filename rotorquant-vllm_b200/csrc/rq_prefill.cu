@@ -35,7 +35,6 @@ constexpr int kPfThreads = 128;
 constexpr int kPfRows = 128;          // MMA M
 constexpr int kPfKeys = 128;          // keys per tile (MMA N of S, K extent of P V)
 constexpr uint32_t kTmemCols = 256;   // S: columns 0..127 (int32), O: columns 128..255 (fp32)
-constexpr long long kWaitCycles = 2000000000LL;   // ~1 s bound on every barrier wait
 
 struct PrefillParams {
     const void* q;
@@ -61,27 +60,6 @@ struct PrefillParams {
 
 // ---- PTX wrappers ------------------------------------------------------------------------
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-// Wait for the phase with the given parity to complete; false if the bound expired.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    const long long start = clock64();
-    for (;;) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if (clock64() - start > kWaitCycles) return false;
-    }
-}
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
