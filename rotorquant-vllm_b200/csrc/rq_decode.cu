@@ -4,16 +4,18 @@
 // Triton kernel (one program per (sequence, query head), CUDA-core dot products, no split-KV)
 // and the two dense 128x128 rotations its launcher runs around it.
 //
-// Work decomposition.  One CTA = one (sequence, KV head, context split); its eight warps walk
-// the split's 16-token tiles round robin, each with a private cp.async ring in shared memory,
-// so the 136 payload bytes of a (token, KV head) are read from HBM exactly once for all query
-// heads of the GQA group.  A second small kernel merges the splits, rounds, and applies R.
+// Work decomposition.  Three launches: a one-CTA prefix sum of the tiles per sequence, the
+// streaming kernel (see below: every warp of a fixed grid streams an equal share of the
+// (sequence, 16-token tile) space for one KV head, with a private cp.async ring, so the 136
+// payload bytes of a (token, KV head) are read from HBM exactly once for all query heads of the
+// GQA group), and a merge kernel that combines the partial results, rounds, and applies R.
 //
 // Arithmetic (matches "reference decompress + SDPA"):
 //   q_rot   = round_T(q @ R^T)            exact FMA chain per 4x4 block, computed in the prologue
 //   K, V    = round_T(centroid[idx]*norm) exactly the decompressed values: each token gets a
 //             table of its 8/16 rounded products, elements are fetched from it with PRMT
-//   scores  = tensor-core mma (bf16/f16 inputs, fp32 accumulate), exp2-domain online softmax
+//   scores  = int8 tensor-core mma over 15-bit integer images of q_rot and K (exact for K, 2^-14
+//             of the row maximum for q), fp32 scaling, exp2-domain online softmax
 //   P @ V   = tensor-core mma with P split into hi + lo parts (two T-precision terms, ~16 bits),
 //             fp32 accumulate
 //   out     = round_T(round_T(o / l) @ R)  in the merge kernel
@@ -49,14 +51,18 @@ struct DecodeParams {
     float qk_scale;                        // sm_scale * log2(e)
     int H, Hq, G;                          // KV heads, query heads, Hq / H
     int head_groups;                       // ceil(G / 8)
-    int tiles_per_split;
-    int num_splits;
-    float* ws_o;                           // [seq][Hq][split][128]
-    float* ws_m;                           // [seq][Hq][split]
+    float* ws_o;                           // [row][8 heads][128], row = (group + sequence) * J + item
+    float* ws_m;                           // [row][8 heads]
     float* ws_l;
     // merge
     void* out;
     int64_t o_stride_seq, o_stride_head;
+    // streaming kernel
+    const int32_t* tile_prefix;           // [num_seqs + 1] exclusive prefix of tiles per sequence
+    int num_seqs;
+    int stream_warps;                     // warps of the streaming grid (multiple of 8)
+    int stream_groups;                    // groups of J warps; each owns one piece of the tile space
+    int bs_shift;                         // log2(block_size) when it is a power of two, else -1
 };
 
 // ---- small PTX wrappers ------------------------------------------------------
@@ -289,484 +295,533 @@ struct __align__(16) Stage {
     uint8_t v[kTile][kVPitch];         // V indices, padded rows (conflict-free 16-byte reads)
     float norms[2 * kTile];            // [0..15] K norms, [16..31] V norms
 };
-struct __align__(256) WarpSmem {
-    uint16_t vt[kTile][kHeadDim];      // decompressed V tile, 16-byte chunks XOR-swizzled by token
+// ---- the streaming kernel ---------------------------------------------------------------------
+//
+// Work is the linear space of (sequence, 16-token tile).  It is cut into equal contiguous pieces,
+// one per GROUP of J warps (J = KV heads x head groups; warp j of a group streams item j of the
+// piece), on a fixed-size grid of two 8-warp CTAs per SM.  Every warp streams the same number of
+// tiles whatever the batch looks like: no wave quantisation, no idle tail, and the per-sequence
+// set-up is paid once per piece.  The warps of a group read the same tokens at about the same
+// time, so neighbouring heads share the 128-byte lines that DRAM delivers (a warp-per-head order
+// that spreads the heads in time was measured to double DRAM traffic).  Warps never synchronise
+// with each other.  A piece that crosses into the next sequence yields one partial result per
+// part; part (group, sequence) of item j is stored at workspace row (group + sequence) * J + j,
+// unique because group and sequence only grow along the space.
+
+struct __align__(256) StreamWarpSmem {
+    uint16_t vt[kTile][kHeadDim];      // V transposition tile; also Q set-up scratch and output stage
     Stage stage[kStages];
-    uint32_t tbl_k[kTile][8];          // per-token K integer planes (4 or 8 registers used)
-    uint32_t tbl_v[kTile][8];          // per-token V value planes
-    float k_unscale[kTile];            // 2^(e-13) of every K table
+    uint32_t tbl_k[kTile][8];
+    uint32_t tbl_v[kTile][8];
+    float k_unscale[kTile];
+    float cb[2][16];                   // K and V codebooks (per warp: no CTA-wide barrier needed)
 };
-static_assert(sizeof(WarpSmem) >= sizeof(float) * (kHeadsPerCta * kHeadDim + 2 * kHeadsPerCta),
-              "the per-warp area is reused for the cross-warp merge");
+static_assert(sizeof(StreamWarpSmem::vt) >= 2 * kHeadsPerCta * kHeadDim, "vt holds the query byte planes");
+static_assert(sizeof(StreamWarpSmem::vt) >= sizeof(float) * kHeadsPerCta * kHeadDim, "vt stages the partial output");
 
-struct __align__(256) DecodeSmem {
-    WarpSmem warp[kDecodeWarps];
-    uint8_t q_hi[kHeadsPerCta][kHeadDim];   // signed byte planes of the rotated queries' integer
-    uint8_t q_lo[kHeadsPerCta][kHeadDim];   // image (256 * hi + lo); element d stored at index d ^ 1
-    float q_unscale[kHeadsPerCta];
-    float cb[2][16];                         // K and V codebooks
-};
+// One 16-token tile: tables, S = Q K^T (int8), online softmax, V transposition, O += P V.
+template <typename T, int KB, int VB>
+__device__ __forceinline__ void stream_tile(StreamWarpSmem& ws, const Stage& st, int n_valid, int lane,
+                                            int g, int tig, const uint32_t (&qa)[4][4], float q_factor,
+                                            float& m_run, float& l_run, float (&o_acc)[8][4], int tv,
+                                            int vhalf, uint32_t vt_store_base, uint32_t lm_base) {
+    // ---- per-token tables: lane builds one half (lane >> 4) of the K and of the V table of
+    //      token (lane & 15), so both half-warps run the same instructions ----
+    {
+        const int i = lane & 15, hb = lane >> 4;
+        const bool valid = i < n_valid;
+        const float norm_k = valid ? st.norms[i] : 0.0f;
+        const float norm_v = valid ? st.norms[kTile + i] : 0.0f;
+        constexpr int NKH = (1 << KB) / 2, NVH = (1 << VB) / 2;
+        float unscale;
+        uint32_t lo[NKH / 4], hi[NKH / 4];
+        build_half_int_table<T, NKH>(&ws.cb[0][hb * NKH], norm_k, lo, hi, unscale);
+        uint32_t vlo[NVH / 4], vhi[NVH / 4];
+        build_half_value_table<T, NVH>(&ws.cb[1][hb * NVH], norm_v, vlo, vhi);
+#pragma unroll
+        for (int r = 0; r < NKH / 4; ++r) {
+            ws.tbl_k[i][hb * (NKH / 4) + r] = lo[r];
+            ws.tbl_k[i][2 * (NKH / 4) + hb * (NKH / 4) + r] = hi[r];
+        }
+#pragma unroll
+        for (int r = 0; r < NVH / 4; ++r) {
+            ws.tbl_v[i][hb * (NVH / 4) + r] = vlo[r];
+            ws.tbl_v[i][2 * (NVH / 4) + hb * (NVH / 4) + r] = vhi[r];
+        }
+        if (hb == 0) ws.k_unscale[i] = unscale;
+    }
+    __syncwarp();
 
-// ---- the split kernel -------------------------------------------------------------
+    // ---- S = Q K^T on the int8 path: rows = heads (g), columns = tokens ----
+    float sc[4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+        // acc_h = [Qhi; Qlo] . Khi, acc_l = [Qhi; Qlo] . Klo: entries 0,1 are the Qhi rows,
+        // entries 2,3 the Qlo rows of the same head and the same two tokens
+        int acc_h[4] = {0, 0, 0, 0}, acc_l[4] = {0, 0, 0, 0};
+        const int tok = g + 8 * nt;
+        const uint4 kw = *reinterpret_cast<const uint4*>(&st.k[tok][16 * tig]);
+        const Table<KB> tk = load_table<KB>(ws.tbl_k[tok]);
+        const uint32_t words[4] = {kw.x, kw.y, kw.z, kw.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            uint32_t lo0, hi0, lo1, hi1;
+            lookup4<KB>(tk, words[w], lo0, hi0);            // nibbles 0..3 -> k-slots 4tig..
+            lookup4<KB>(tk, words[w] >> 16, lo1, hi1);      // nibbles 4..7 -> k-slots 16+4tig..
+            mma_s8(acc_h, qa[w][0], qa[w][1], qa[w][2], qa[w][3], hi0, hi1);
+            mma_s8(acc_l, qa[w][0], qa[w][1], qa[w][2], qa[w][3], lo0, lo1);
+        }
+        const float2 ku = *reinterpret_cast<const float2*>(&ws.k_unscale[8 * nt + 2 * tig]);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int t1 = acc_h[c] * 256 + (acc_h[c + 2] + acc_l[c]);
+            const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(acc_l[c + 2]));
+            sc[2 * nt + c] = f * (q_factor * (c ? ku.y : ku.x));
+        }
+    }
+    if (n_valid < kTile) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int tok = 8 * (x >> 1) + 2 * tig + (x & 1);
+            if (tok >= n_valid) sc[x] = -INFINITY;
+        }
+    }
+
+    // ---- online softmax for head g over this thread's 4 columns ----
+    float m_new = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+    m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 1));
+    m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 2));
+    // The running reference m_run only moves when the tile maximum exceeds it by more than 8
+    // (probabilities then stay below 2^8, harmless in fp32), which makes rescaling rare.
+    // Every tile holds at least one valid token, so m_new is finite; m_run starts at -inf.
+    const bool grew = m_new > m_run + 8.0f;
+    if (__any_sync(0xffffffffu, grew)) {
+        const float m_upd = grew ? m_new : m_run;
+        const float alpha = ex2_approx(m_run - m_upd);      // 0 on the first tile, 1 if unchanged
+        l_run *= alpha;
+        // accumulator columns are heads 2tig, 2tig+1: fetch their factors from rows g'
+        const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * tig) * 4);
+        const float a1 = __shfl_sync(0xffffffffu, alpha, (2 * tig + 1) * 4);
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            o_acc[mt][0] *= a0; o_acc[mt][1] *= a1;
+            o_acc[mt][2] *= a0; o_acc[mt][3] *= a1;
+        }
+        m_run = m_upd;
+    }
+    float pr[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        pr[c] = ex2_approx(sc[c] - m_run);
+        l_run += pr[c];
+    }
+    // P as mma B operand (k = tokens 2tig,2tig+1 | 2tig+8,2tig+9; n = head g), hi + lo parts
+    const uint32_t ph0 = pack_pair<T>(pr[0], pr[1]), ph1 = pack_pair<T>(pr[2], pr[3]);
+    const float2 h0 = unpack_pair<T>(ph0), h1 = unpack_pair<T>(ph1);
+    const uint32_t pl0 = pack_pair<T>(pr[0] - h0.x, pr[1] - h0.y);
+    const uint32_t pl1 = pack_pair<T>(pr[2] - h1.x, pr[3] - h1.y);
+
+    // ---- decompress V into the transposition buffer: lane = (token tv, half row) ----
+    {
+        const Table<VB> tb = load_table<VB>(ws.tbl_v[tv]);
+        const uint4 va = *reinterpret_cast<const uint4*>(&st.v[tv][32 * vhalf]);
+        const uint4 vb = *reinterpret_cast<const uint4*>(&st.v[tv][32 * vhalf + 16]);
+        const uint32_t words[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            uint32_t lo0, hi0, lo1, hi1;
+            lookup4<VB>(tb, words[w], lo0, hi0);
+            lookup4<VB>(tb, words[w] >> 16, lo1, hi1);
+            // chunk (8*vhalf + w) ^ (tv & 7): vt rows are 256-byte aligned, so XOR the address
+            st_shared_v4(vt_store_base ^ (16u * w), prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
+                         prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
+        }
+    }
+    __syncwarp();
+
+    // ---- O^T += V^T P^T : rows = 16 head-dim positions per m-tile, columns = heads ----
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, lm_base ^ (32u * mt));
+        mma16816<T>(o_acc[mt], a[0], a[1], a[2], a[3], ph0, ph1);
+        mma16816<T>(o_acc[mt], a[0], a[1], a[2], a[3], pl0, pl1);
+    }
+}
+
+// Tiles of every sequence as an exclusive prefix sum: prefix[s] = sum_{s' < s} ceil(len[s'] / 16).
+__global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num_seqs,
+                                   int32_t* __restrict__ prefix) {
+    __shared__ int warp_sums[32];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < num_seqs; base += blockDim.x) {
+        const int s = base + threadIdx.x;
+        const int n = s < num_seqs ? (max(__ldg(seq_lens + s), 0) + kTile - 1) / kTile : 0;
+        int incl = n;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((threadIdx.x & 31) >= o) incl += v;
+        }
+        if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        int before = carry;
+        for (int w = 0; w < (threadIdx.x >> 5); ++w) before += warp_sums[w];
+        if (s < num_seqs) prefix[s] = before + incl - n;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = before + incl;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) prefix[num_seqs] = carry;
+}
 
 template <typename T, int KB, int VB>
 __global__ void __launch_bounds__(kDecodeThreads, 2)
-decode_split_kernel(const DecodeParams p) {
+decode_stream_kernel(const DecodeParams p) {
     extern __shared__ __align__(256) uint8_t smem_raw[];
-    DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(smem_raw);
-
-    const int split = blockIdx.x;
-    const int kvh = blockIdx.y / p.head_groups;
-    const int hg = blockIdx.y % p.head_groups;
-    const int seq = blockIdx.z;
-    const int heads_here = min(kHeadsPerCta, p.G - hg * kHeadsPerCta);
-    const int first_qh = kvh * p.G + hg * kHeadsPerCta;
-
-    int seq_len = __ldg(p.seq_lens + seq);
-    seq_len = max(seq_len, 0);
-    const int total_tiles = (seq_len + kTile - 1) / kTile;
-    const int tile_begin = split * p.tiles_per_split;
-    const int tile_end = min(total_tiles, tile_begin + p.tiles_per_split);
-    if (tile_begin >= tile_end) return;        // uniform for the CTA
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    StreamWarpSmem& ws = reinterpret_cast<StreamWarpSmem*>(smem_raw)[warp];
     const int g = lane >> 2, tig = lane & 3;
 
-    // ---- per-warp streaming state ----
-    WarpSmem& ws = sm.warp[warp];
-    const SlotLayout lay = slot_layout(p.H);
-    const bool fast_bt = (p.block_size % kTile) == 0;
-    const int32_t* bt_row = p.block_table + seq * p.bt_stride;
-    const int v_align = (lay.v_idx % 16 == 0) ? 16 : ((lay.v_idx % 8 == 0) ? 8 : 4);
+    // ---- this warp's piece: warp = (group, item); a group of J consecutive warps walks one
+    //      range of the (sequence, tile) space, one warp per (KV head, head group) ----
+    const int J = p.H * p.head_groups;                         // items per sequence
+    const int64_t total = __ldg(p.tile_prefix + p.num_seqs);   // tiles of all sequences
+    const int64_t wq = static_cast<int64_t>(blockIdx.x) * kDecodeWarps + warp;
+    const int64_t group = wq / J;
+    const int item = static_cast<int>(wq % J);
+    if (group >= p.stream_groups) return;
+    int64_t x = group * total / p.stream_groups;
+    const int64_t x_end = (group + 1) * total / p.stream_groups;
+    if (x >= x_end) return;
 
-    auto clamp_block = [&](int64_t blk) -> int64_t {
-        return blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
-    };
-    // fast path (block_size a multiple of 16): the 16 slots of a tile are contiguous
-    auto phys_slot0 = [&](int tile) -> int64_t {
-        const int t0 = tile * kTile;
-        return clamp_block(__ldg(bt_row + t0 / p.block_size)) * p.block_size + (t0 % p.block_size);
-    };
-    auto token_slot = [&](int tile, int i) -> int64_t {      // general path: one lookup per token
-        const int t = min(tile * kTile + i, seq_len - 1);
-        return clamp_block(__ldg(bt_row + t / p.block_size)) * p.block_size + (t % p.block_size);
-    };
-
-    // Per-lane source offsets (bytes from the tile's first slot) and shared-memory destinations
-    // (bytes from the stage) of this lane's copies; fixed for the whole kernel.
-    const uint32_t tb = static_cast<uint32_t>(p.total_bytes);
-    const uint32_t src_k = (lane >> 2) * tb + kvh * kHalfDim + 16 * (lane & 3);      // + 8*tb for copy 2
-    const uint32_t dst_k = (lane >> 2) * kHalfDim + 16 * (lane & 3);
-    const uint32_t dst_v16 = sizeof(Stage::k) + (lane >> 2) * kVPitch + 16 * (lane & 3);
-    const uint32_t src_n = (lane & 15) * tb + ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh;
-    const uint32_t dst_n = sizeof(Stage::k) + sizeof(Stage::v) + 4 * lane;
-
-    auto issue = [&](int tile, int s, int64_t slot0) {
-        uint8_t* stg = reinterpret_cast<uint8_t*>(&ws.stage[s]);
-        if (fast_bt) {
-            const uint8_t* base = p.cache + slot0 * p.total_bytes;
-            cp_async16(stg + dst_k, base + src_k);
-            cp_async16(stg + dst_k + 8 * kHalfDim, base + src_k + 8 * tb);
-            if (v_align == 16) {
-                cp_async16(stg + dst_v16, base + src_k + lay.v_idx);
-                cp_async16(stg + dst_v16 + 8 * kVPitch, base + src_k + 8 * tb + lay.v_idx);
-            } else if (v_align == 8) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int c = lane + 32 * j, i = c >> 3, part = c & 7;
-                    cp_async8(stg + sizeof(Stage::k) + i * kVPitch + 8 * part,
-                              base + i * tb + lay.v_idx + kvh * kHalfDim + 8 * part);
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int c = lane + 32 * j, i = c >> 4, part = c & 15;
-                    cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
-                              base + i * tb + lay.v_idx + kvh * kHalfDim + 4 * part);
-                }
-            }
-            cp_async4(stg + dst_n, base + src_n);
-            return;
-        }
-        // general path: tokens of a tile may sit in different blocks
-        const uint8_t* head_base = p.cache + kvh * kHalfDim;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int c = lane + 32 * j, i = c >> 2, part = c & 3;
-            const uint8_t* src = head_base + token_slot(tile, i) * p.total_bytes + 16 * part;
-            cp_async16(stg + i * kHalfDim + 16 * part, src + lay.k_idx);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int c = lane + 32 * j, i = c >> 4, part = c & 15;
-            cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
-                      head_base + token_slot(tile, i) * p.total_bytes + lay.v_idx + 4 * part);
-        }
-        cp_async4(stg + dst_n, p.cache + token_slot(tile, lane & 15) * p.total_bytes +
-                                   ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh);
-    };
-
-    // online-softmax state of head g (partial over this thread's token columns)
-    float m_run = -INFINITY, l_run = 0.0f;
-    float o_acc[8][4];
-#pragma unroll
-    for (int mt = 0; mt < 8; ++mt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) o_acc[mt][c] = 0.0f;
-
-    const int first_tile = tile_begin + warp;
-    const int n_my = first_tile < tile_end ? (tile_end - first_tile + kDecodeWarps - 1) / kDecodeWarps : 0;
-
-    // prefetch pipeline: block-table entry of the next tile to issue is read one step ahead
-    int pf_it = 0, pf_stage = 0;
-    int64_t pf_slot0 = (n_my > 0 && fast_bt) ? phys_slot0(first_tile) : 0;
-    auto issue_next = [&]() {
-        if (pf_it < n_my) {
-            const int tile = first_tile + pf_it * kDecodeWarps;
-            issue(tile, pf_stage, pf_slot0);
-            ++pf_it;
-            pf_stage = pf_stage + 1 == kStages ? 0 : pf_stage + 1;
-            if (pf_it < n_my && fast_bt) pf_slot0 = phys_slot0(first_tile + pf_it * kDecodeWarps);
-        }
-        cp_async_commit();
-    };
-#pragma unroll 1
-    for (int s = 0; s < kStages - 1; ++s) issue_next();
-
-    // (the first tiles are now in flight; their latency overlaps the query set-up below)
-    // ---- prologue: codebooks; q_rot = round_T(q @ R^T) as int16 planes in shared memory ----
-    if (tid < 32) {
-        const int kv = tid >> 4, i = tid & 15;
+    if (lane < 32) {
+        const int kv = lane >> 4, i = lane & 15;
         const int n = kv ? (1 << VB) : (1 << KB);
-        sm.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
+        ws.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
     }
-    {
-        // warp h rotates head h: lane = one 4x4 block
-        const int h = warp, blk = lane;
-        float r[4] = {0.f, 0.f, 0.f, 0.f};
-        if (h < heads_here) {
-            const T* qp = static_cast<const T*>(p.q) + seq * p.q_stride_seq +
-                          static_cast<int64_t>(first_qh + h) * p.q_stride_head + 4 * blk;
-            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(qp));
-            const float2 x01 = unpack_pair<T>(raw.x), x23 = unpack_pair<T>(raw.y);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float4 rr = __ldg(reinterpret_cast<const float4*>(
-                    p.rotation + (4 * blk + j) * kHeadDim + 4 * blk));
-                float acc = __fmul_rn(x01.x, rr.x);
-                acc = __fmaf_rn(x01.y, rr.y, acc);
-                acc = __fmaf_rn(x23.x, rr.z, acc);
-                acc = __fmaf_rn(x23.y, rr.w, acc);
-                r[j] = round_to<T>(acc);
-            }
-        }
-        float mx = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        const bool ok = mx >= 1.0e-30f && mx <= 3.0e38f;
-        const int e = ok ? exponent_of(mx) : 0;
-        const float scale = ok ? pow2i(13 - e) : 0.0f;
-        int qu[4];      // integer image + 128: byte 1 = signed high digit, byte 0 ^ 0x80 = signed low digit
-#pragma unroll
-        for (int j = 0; j < 4; ++j) qu[j] = __float2int_rn(fmaf(r[j], scale, 128.0f));
-        // element d lives at index d ^ 1: byte order (1, 0, 3, 2)
-        const uint32_t a = prmt(qu[1], qu[0], 0x5140), b = prmt(qu[3], qu[2], 0x5140);
-        *reinterpret_cast<uint32_t*>(&sm.q_lo[h][4 * blk]) = prmt(a, b, 0x5410) ^ 0x80808080u;
-        *reinterpret_cast<uint32_t*>(&sm.q_hi[h][4 * blk]) = prmt(a, b, 0x7632);
-        if (lane == 0) sm.q_unscale[h] = ok ? pow2i(e - 13) : 0.0f;
-    }
-    __syncthreads();
-
-    // Query fragments (mma A operand): rows 0..7 carry the high digits of heads 0..7, rows 8..15
-    // the low digits of the same heads, so one MMA yields Qhi.K and Qlo.K for a K plane.  In
-    // k-step w the thread supplies k-slots 4tig..4tig+3 and 16+4tig..16+4tig+3, which this kernel
-    // maps to the elements of nibbles 0..3 and 4..7 of word w of its 16-byte chunk of a K row.
-    uint32_t qa[4][4];
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-        const int off = 32 * tig + 8 * w;
-        qa[w][0] = *reinterpret_cast<const uint32_t*>(&sm.q_hi[g][off]);
-        qa[w][1] = *reinterpret_cast<const uint32_t*>(&sm.q_lo[g][off]);
-        qa[w][2] = *reinterpret_cast<const uint32_t*>(&sm.q_hi[g][off + 4]);
-        qa[w][3] = *reinterpret_cast<const uint32_t*>(&sm.q_lo[g][off + 4]);
-    }
-    const float q_factor = sm.q_unscale[g] * p.qk_scale;
-
-
-    // per-lane constants of the V transpose: this lane decompresses half a row of token tv ...
+    const SlotLayout lay = slot_layout(p.H);
+    const bool fast_bt = p.bs_shift >= 4;                      // power-of-two block size >= 16
+    const int v_align = (lay.v_idx % 16 == 0) ? 16 : ((lay.v_idx % 8 == 0) ? 8 : 4);
+    const uint32_t tb = static_cast<uint32_t>(p.total_bytes);
     const int tv = lane & 15, vhalf = lane >> 4;
-    // ... and feeds ldmatrix with row (lane & 7) of 8x8 matrix (lane >> 3)
     const int lm_tok = (lane & 7) + ((lane & 16) ? 8 : 0);
     const int lm_chunk = (lane >> 3) & 1;
-    // generic addresses whose low byte already holds the swizzle; chunk selection is one XOR
-    const uint32_t vt_store_base = static_cast<uint32_t>(__cvta_generic_to_shared(&ws.vt[tv][0])) +
-                                   128u * vhalf + 16u * (tv & 7);
-    const uint32_t lm_base = static_cast<uint32_t>(__cvta_generic_to_shared(&ws.vt[lm_tok][0])) +
-                             16u * (lm_chunk ^ (lm_tok & 7));
+    const uint32_t vt_store_base = smem_u32(&ws.vt[tv][0]) + 128u * vhalf + 16u * (tv & 7);
+    const uint32_t lm_base = smem_u32(&ws.vt[lm_tok][0]) + 16u * (lm_chunk ^ (lm_tok & 7));
 
-    int cur_stage = 0;
-#pragma unroll 1
-    for (int it = 0; it < n_my; ++it) {
-        issue_next();
-        cp_async_wait<kStages - 1>();
-        __syncwarp();
-        const Stage& st = ws.stage[cur_stage];
-        cur_stage = cur_stage + 1 == kStages ? 0 : cur_stage + 1;
-        const int tile = first_tile + it * kDecodeWarps;
-        const int n_valid = min(kTile, seq_len - tile * kTile);
-
-        // ---- per-token tables: lane builds one half (lane >> 4) of the K and of the V table of
-        //      token (lane & 15), so both half-warps run the same instructions ----
-        {
-            const int i = lane & 15, hb = lane >> 4;
-            const bool valid = i < n_valid;
-            const float norm_k = valid ? st.norms[i] : 0.0f;
-            const float norm_v = valid ? st.norms[kTile + i] : 0.0f;
-            constexpr int NKH = (1 << KB) / 2, NVH = (1 << VB) / 2;
-            float unscale;
-            uint32_t lo[NKH / 4], hi[NKH / 4];
-            build_half_int_table<T, NKH>(&sm.cb[0][hb * NKH], norm_k, lo, hi, unscale);
-            uint32_t vlo[NVH / 4], vhi[NVH / 4];
-            build_half_value_table<T, NVH>(&sm.cb[1][hb * NVH], norm_v, vlo, vhi);
-#pragma unroll
-            for (int r = 0; r < NKH / 4; ++r) {
-                ws.tbl_k[i][hb * (NKH / 4) + r] = lo[r];
-                ws.tbl_k[i][2 * (NKH / 4) + hb * (NKH / 4) + r] = hi[r];
-            }
-#pragma unroll
-            for (int r = 0; r < NVH / 4; ++r) {
-                ws.tbl_v[i][hb * (NVH / 4) + r] = vlo[r];
-                ws.tbl_v[i][2 * (NVH / 4) + hb * (NVH / 4) + r] = vhi[r];
-            }
-            if (hb == 0) ws.k_unscale[i] = unscale;
-        }
-        __syncwarp();
-
-        // ---- S = Q K^T on the int8 path: rows = heads (g), columns = tokens ----
-        float sc[4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            // acc_h = [Qhi; Qlo] . Khi, acc_l = [Qhi; Qlo] . Klo: entries 0,1 are the Qhi rows,
-            // entries 2,3 the Qlo rows of the same head and the same two tokens
-            int acc_h[4] = {0, 0, 0, 0}, acc_l[4] = {0, 0, 0, 0};
-            const int tok = g + 8 * nt;
-            const uint4 kw = *reinterpret_cast<const uint4*>(&st.k[tok][16 * tig]);
-            const Table<KB> tk = load_table<KB>(ws.tbl_k[tok]);
-            const uint32_t words[4] = {kw.x, kw.y, kw.z, kw.w};
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                uint32_t lo0, hi0, lo1, hi1;
-                lookup4<KB>(tk, words[w], lo0, hi0);            // nibbles 0..3 -> k-slots 4tig..
-                lookup4<KB>(tk, words[w] >> 16, lo1, hi1);      // nibbles 4..7 -> k-slots 16+4tig..
-                mma_s8(acc_h, qa[w][0], qa[w][1], qa[w][2], qa[w][3], hi0, hi1);
-                mma_s8(acc_l, qa[w][0], qa[w][1], qa[w][2], qa[w][3], lo0, lo1);
-            }
-            const float2 ku = *reinterpret_cast<const float2*>(&ws.k_unscale[8 * nt + 2 * tig]);
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int t1 = acc_h[c] * 256 + (acc_h[c + 2] + acc_l[c]);
-                const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(acc_l[c + 2]));
-                sc[2 * nt + c] = f * (q_factor * (c ? ku.y : ku.x));
-            }
-        }
-        if (n_valid < kTile) {
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const int tok = 8 * (x >> 1) + 2 * tig + (x & 1);
-                if (tok >= n_valid) sc[x] = -INFINITY;
-            }
-        }
-
-        // ---- online softmax for head g over this thread's 4 columns ----
-        float m_new = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-        m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 1));
-        m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 2));
-        // The running reference m_run only moves when the tile maximum exceeds it by more than 8
-        // (probabilities then stay below 2^8, harmless in fp32), which makes rescaling rare.
-        // Every tile holds at least one valid token, so m_new is finite; m_run starts at -inf.
-        const bool grew = m_new > m_run + 8.0f;
-        if (__any_sync(0xffffffffu, grew)) {
-            const float m_upd = grew ? m_new : m_run;
-            const float alpha = ex2_approx(m_run - m_upd);      // 0 on the first tile, 1 if unchanged
-            l_run *= alpha;
-            // accumulator columns are heads 2tig, 2tig+1: fetch their factors from rows g'
-            const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * tig) * 4);
-            const float a1 = __shfl_sync(0xffffffffu, alpha, (2 * tig + 1) * 4);
-#pragma unroll
-            for (int mt = 0; mt < 8; ++mt) {
-                o_acc[mt][0] *= a0; o_acc[mt][1] *= a1;
-                o_acc[mt][2] *= a0; o_acc[mt][3] *= a1;
-            }
-            m_run = m_upd;
-        }
-        float pr[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            pr[c] = ex2_approx(sc[c] - m_run);
-            l_run += pr[c];
-        }
-        // P as mma B operand (k = tokens 2tig,2tig+1 | 2tig+8,2tig+9; n = head g), hi + lo parts
-        const uint32_t ph0 = pack_pair<T>(pr[0], pr[1]), ph1 = pack_pair<T>(pr[2], pr[3]);
-        const float2 h0 = unpack_pair<T>(ph0), h1 = unpack_pair<T>(ph1);
-        const uint32_t pl0 = pack_pair<T>(pr[0] - h0.x, pr[1] - h0.y);
-        const uint32_t pl1 = pack_pair<T>(pr[2] - h1.x, pr[3] - h1.y);
-
-        // ---- decompress V into the transposition buffer: lane = (token tv, half row) ----
-        {
-            const Table<VB> tb = load_table<VB>(ws.tbl_v[tv]);
-            const uint4 va = *reinterpret_cast<const uint4*>(&st.v[tv][32 * vhalf]);
-            const uint4 vb = *reinterpret_cast<const uint4*>(&st.v[tv][32 * vhalf + 16]);
-            const uint32_t words[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-#pragma unroll
-            for (int w = 0; w < 8; ++w) {
-                uint32_t lo0, hi0, lo1, hi1;
-                lookup4<VB>(tb, words[w], lo0, hi0);
-                lookup4<VB>(tb, words[w] >> 16, lo1, hi1);
-                // chunk (8*vhalf + w) ^ (tv & 7): vt rows are 256-byte aligned, so XOR the address
-                st_shared_v4(vt_store_base ^ (16u * w), prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
-                             prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
-            }
-        }
-        __syncwarp();
-
-        // ---- O^T += V^T P^T : rows = 16 head-dim positions per m-tile, columns = heads ----
-#pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            uint32_t a[4];
-            ldmatrix_x4_trans(a, lm_base ^ (32u * mt));
-            mma16816<T>(o_acc[mt], a[0], a[1], a[2], a[3], ph0, ph1);
-            mma16816<T>(o_acc[mt], a[0], a[1], a[2], a[3], pl0, pl1);
-        }
-        __syncwarp();        // the stage, the tables and vt may be overwritten from here on
+    // sequence holding position x: first s with prefix[s + 1] > x
+    int seq = 0;
+    for (int base = 0; base < p.num_seqs; base += 32) {
+        const int s = base + lane;
+        const int64_t end = s < p.num_seqs ? __ldg(p.tile_prefix + s + 1) : INT64_MAX;
+        const unsigned hit = __ballot_sync(0xffffffffu, end > x);
+        if (hit) { seq = base + __ffs(hit) - 1; break; }
     }
-    cp_async_wait<0>();
 
-    // ---- cross-warp merge inside the CTA (each warp parks its state in its own area) ----
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    __syncwarp();
-    {
-        float* area = reinterpret_cast<float*>(&ws);
-        float* o_s = area;                                  // [8 heads][128]
-        float* m_s = area + kHeadsPerCta * kHeadDim;        // [8]
-        float* l_s = m_s + kHeadsPerCta;
-        if (tig == 0) { m_s[g] = m_run; l_s[g] = l_run; }
+#pragma unroll 1
+    while (x < x_end && seq < p.num_seqs) {
+        // ---- the part of this piece inside one sequence ----
+        const int pre = __ldg(p.tile_prefix + seq), n_s = __ldg(p.tile_prefix + seq + 1) - pre;
+        if (n_s <= 0 || x >= static_cast<int64_t>(pre) + n_s) { ++seq; continue; }
+        const int t_begin = static_cast<int>(x - pre);
+        const int64_t reach = t_begin + (x_end - x);
+        const int t_end = reach < n_s ? static_cast<int>(reach) : n_s;
+        const int kvh = item / p.head_groups, hg = item % p.head_groups;
+        const int heads_here = min(kHeadsPerCta, p.G - hg * kHeadsPerCta);
+        const int first_qh = kvh * p.G + hg * kHeadsPerCta;
+        const int seq_len = max(__ldg(p.seq_lens + seq), 0);
+        const int32_t* bt_row = p.block_table + seq * p.bt_stride;
+
+        auto clamp_block = [&](int64_t blk) -> int64_t {
+            return blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
+        };
+        auto tile_base = [&](int tile) -> const uint8_t* {     // fast path: first slot of the tile
+            const int t0 = tile * kTile;
+            const int64_t blk = clamp_block(__ldg(bt_row + (t0 >> p.bs_shift)));
+            return p.cache + ((blk << p.bs_shift) + (t0 & (p.block_size - 1))) * p.total_bytes;
+        };
+        auto token_ptr = [&](int tile, int i) -> const uint8_t* {   // general path
+            const int t = min(tile * kTile + i, seq_len - 1);
+            const int64_t blk = clamp_block(__ldg(bt_row + t / p.block_size));
+            return p.cache + (blk * p.block_size + (t % p.block_size)) * p.total_bytes;
+        };
+        const uint32_t src_k = (lane >> 2) * tb + kvh * kHalfDim + 16 * (lane & 3);
+        const uint32_t dst_k = (lane >> 2) * kHalfDim + 16 * (lane & 3);
+        const uint32_t dst_v16 = sizeof(Stage::k) + (lane >> 2) * kVPitch + 16 * (lane & 3);
+        const uint32_t src_n = (lane & 15) * tb + ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh;
+        const uint32_t dst_n = sizeof(Stage::k) + sizeof(Stage::v) + 4 * lane;
+        auto issue = [&](int tile, int s, const uint8_t* base) {
+            uint8_t* stg = reinterpret_cast<uint8_t*>(&ws.stage[s]);
+            if (fast_bt) {
+                cp_async16(stg + dst_k, base + src_k);
+                cp_async16(stg + dst_k + 8 * kHalfDim, base + src_k + 8 * tb);
+                if (v_align == 16) {
+                    cp_async16(stg + dst_v16, base + src_k + lay.v_idx);
+                    cp_async16(stg + dst_v16 + 8 * kVPitch, base + src_k + 8 * tb + lay.v_idx);
+                } else if (v_align == 8) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int c = lane + 32 * j, i = c >> 3, part = c & 7;
+                        cp_async8(stg + sizeof(Stage::k) + i * kVPitch + 8 * part,
+                                  base + i * tb + lay.v_idx + kvh * kHalfDim + 8 * part);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int c = lane + 32 * j, i = c >> 4, part = c & 15;
+                        cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
+                                  base + i * tb + lay.v_idx + kvh * kHalfDim + 4 * part);
+                    }
+                }
+                cp_async4(stg + dst_n, base + src_n);
+                return;
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = lane + 32 * j, i = c >> 2, part = c & 3;
+                cp_async16(stg + i * kHalfDim + 16 * part,
+                           token_ptr(tile, i) + lay.k_idx + kvh * kHalfDim + 16 * part);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c = lane + 32 * j, i = c >> 4, part = c & 15;
+                cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
+                          token_ptr(tile, i) + lay.v_idx + kvh * kHalfDim + 4 * part);
+            }
+            cp_async4(stg + dst_n, token_ptr(tile, lane & 15) +
+                                       ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh);
+        };
+
+        // first tiles in flight before the query set-up; the block-table entry of the tile after
+        // the one being issued is read one step ahead so that its latency is off the issue path
+        int pf_tile = t_begin, pf_stage = 0;
+        const uint8_t* pf_base = fast_bt ? tile_base(t_begin) : nullptr;
+        auto issue_next = [&]() {
+            if (pf_tile < t_end) {
+                issue(pf_tile, pf_stage, pf_base);
+                ++pf_tile;
+                pf_stage = pf_stage + 1 == kStages ? 0 : pf_stage + 1;
+                if (fast_bt && pf_tile < t_end) pf_base = tile_base(pf_tile);
+            }
+            cp_async_commit();
+        };
+#pragma unroll 1
+        for (int s = 0; s < kStages - 1; ++s) issue_next();
+
+        // ---- queries of this item: rotate, round, quantise to signed byte planes (scratch: vt) ----
+        uint8_t* q_hi = reinterpret_cast<uint8_t*>(&ws.vt[0][0]);     // [8][128]
+        uint8_t* q_lo = q_hi + kHeadsPerCta * kHeadDim;
+        float my_unscale = 0.0f;                                       // lane g keeps the factor of head g
+#pragma unroll 1
+        for (int h = 0; h < kHeadsPerCta; ++h) {
+            float r[4] = {0.f, 0.f, 0.f, 0.f};
+            if (h < heads_here) {
+                const T* qp = static_cast<const T*>(p.q) + seq * p.q_stride_seq +
+                              static_cast<int64_t>(first_qh + h) * p.q_stride_head + 4 * lane;
+                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(qp));
+                const float2 x01 = unpack_pair<T>(raw.x), x23 = unpack_pair<T>(raw.y);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 rr = __ldg(reinterpret_cast<const float4*>(
+                        p.rotation + (4 * lane + j) * kHeadDim + 4 * lane));
+                    float acc = __fmul_rn(x01.x, rr.x);
+                    acc = __fmaf_rn(x01.y, rr.y, acc);
+                    acc = __fmaf_rn(x23.x, rr.z, acc);
+                    acc = __fmaf_rn(x23.y, rr.w, acc);
+                    r[j] = round_to<T>(acc);
+                }
+            }
+            float mx = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const bool ok = mx >= 1.0e-30f && mx <= 3.0e38f;
+            const int e = ok ? exponent_of(mx) : 0;
+            const float scale = ok ? pow2i(13 - e) : 0.0f;
+            int qu[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) qu[j] = __float2int_rn(fmaf(r[j], scale, 128.0f));
+            const uint32_t a = prmt(qu[1], qu[0], 0x5140), b = prmt(qu[3], qu[2], 0x5140);
+            *reinterpret_cast<uint32_t*>(q_lo + h * kHeadDim + 4 * lane) = prmt(a, b, 0x5410) ^ 0x80808080u;
+            *reinterpret_cast<uint32_t*>(q_hi + h * kHeadDim + 4 * lane) = prmt(a, b, 0x7632);
+            if (g == h) my_unscale = ok ? pow2i(e - 13) : 0.0f;
+        }
+        __syncwarp();
+        uint32_t qa[4][4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const int off = g * kHeadDim + 32 * tig + 8 * w;
+            qa[w][0] = *reinterpret_cast<const uint32_t*>(q_hi + off);
+            qa[w][1] = *reinterpret_cast<const uint32_t*>(q_lo + off);
+            qa[w][2] = *reinterpret_cast<const uint32_t*>(q_hi + off + 4);
+            qa[w][3] = *reinterpret_cast<const uint32_t*>(q_lo + off + 4);
+        }
+        const float q_factor = my_unscale * p.qk_scale;
+        __syncwarp();                                  // vt is free for the tile loop
+
+        float m_run = -INFINITY, l_run = 0.0f;
+        float o_acc[8][4];
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) o_acc[mt][c] = 0.0f;
+
+        int cur_stage = 0;
+#pragma unroll 1
+        for (int tile = t_begin; tile < t_end; ++tile) {
+            issue_next();
+            cp_async_wait<kStages - 1>();
+            __syncwarp();
+            const Stage& st = ws.stage[cur_stage];
+            cur_stage = cur_stage + 1 == kStages ? 0 : cur_stage + 1;
+            stream_tile<T, KB, VB>(ws, st, min(kTile, seq_len - tile * kTile), lane, g, tig, qa, q_factor,
+                                   m_run, l_run, o_acc, tv, vhalf, vt_store_base, lm_base);
+            __syncwarp();      // the stage, the tables and vt may be overwritten from here on
+        }
+        cp_async_wait<0>();
+
+        // ---- partial result of this part -> workspace row (warp + item) ----
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        float* o_s = reinterpret_cast<float*>(&ws.vt[0][0]);          // [8 heads][128]
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
-            // row g of m-tile mt is position g of 8-wide chunk 2mt, i.e. head-dim 16mt + (g^1);
-            // row g+8 is the same position of chunk 2mt+1
             const int d = 16 * mt + (g ^ 1);
             o_s[(2 * tig) * kHeadDim + d] = o_acc[mt][0];
             o_s[(2 * tig + 1) * kHeadDim + d] = o_acc[mt][1];
             o_s[(2 * tig) * kHeadDim + d + 8] = o_acc[mt][2];
             o_s[(2 * tig + 1) * kHeadDim + d + 8] = o_acc[mt][3];
         }
-    }
-    __syncthreads();
-    {
-        const int h = tid >> 5, d4 = (tid & 31) * 4;
-        if (h < heads_here) {
-            float m_all = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < kDecodeWarps; ++w) {
-                const float* area = reinterpret_cast<const float*>(&sm.warp[w]);
-                m_all = fmaxf(m_all, area[kHeadsPerCta * kHeadDim + h]);
-            }
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            float l_all = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kDecodeWarps; ++w) {
-                const float* area = reinterpret_cast<const float*>(&sm.warp[w]);
-                const float mw = area[kHeadsPerCta * kHeadDim + h];
-                const float wgt = (mw == -INFINITY) ? 0.0f : exp2f(mw - m_all);
-                const float4 o = *reinterpret_cast<const float4*>(&area[h * kHeadDim + d4]);
-                acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
-                l_all += wgt * area[kHeadsPerCta * kHeadDim + kHeadsPerCta + h];
-            }
-            const int64_t row = (static_cast<int64_t>(seq) * p.Hq + first_qh + h) * p.num_splits + split;
-            *reinterpret_cast<float4*>(p.ws_o + row * kHeadDim + d4) = acc;
-            if ((tid & 31) == 0) { p.ws_m[row] = m_all; p.ws_l[row] = l_all; }
+        __syncwarp();
+        const int64_t row = (group + seq) * J + item;
+#pragma unroll 1
+        for (int h = 0; h < heads_here; ++h) {
+            const float4 v = *reinterpret_cast<const float4*>(&o_s[h * kHeadDim + 4 * lane]);
+            *reinterpret_cast<float4*>(p.ws_o + (row * kHeadsPerCta + h) * kHeadDim + 4 * lane) = v;
         }
+        if (tig == 0 && g < heads_here) {
+            p.ws_m[row * kHeadsPerCta + g] = m_run;
+            p.ws_l[row * kHeadsPerCta + g] = l_run;
+        }
+        __syncwarp();
+
+        x += t_end - t_begin;
+        if (t_end == n_s) ++seq;
     }
 }
 
-// ---- merge kernel: combine splits, normalise, round, rotate back by R ---------------------
-
+// Merge for the streaming kernel: the parts of a (sequence, head) are the groups whose pieces
+// overlap the sequence's tile range; part (group, sequence) of item j lives at row
+// (group + sequence) * J + j.  Warp 0 gathers the running maxima and row sums of up to 32 parts
+// at a time with one load per lane; then every thread sums its head-dim over the parts.
 template <typename T>
 __global__ void __launch_bounds__(kHeadDim)
-decode_merge_kernel(const DecodeParams p) {
+decode_stream_merge_kernel(const DecodeParams p) {
     __shared__ float o_s[kHeadDim];
+    __shared__ float w_s[32];
+    __shared__ float l_s, m_s;
     const int seq = blockIdx.x / p.Hq, qh = blockIdx.x % p.Hq;
-    const int d = threadIdx.x;
-    int seq_len = max(__ldg(p.seq_lens + seq), 0);
-    const int total_tiles = (seq_len + kTile - 1) / kTile;
-    const int n_act = min(p.num_splits, (total_tiles + p.tiles_per_split - 1) / p.tiles_per_split);
-    const int64_t row0 = (static_cast<int64_t>(seq) * p.Hq + qh) * p.num_splits;
-    float m_all = -INFINITY;
-    for (int s = 0; s < n_act; ++s) m_all = fmaxf(m_all, p.ws_m[row0 + s]);
-    float acc = 0.0f, l_all = 0.0f;
-    for (int s = 0; s < n_act; ++s) {
-        const float wgt = exp2f(p.ws_m[row0 + s] - m_all);
-        acc += wgt * p.ws_o[(row0 + s) * kHeadDim + d];
-        l_all += wgt * p.ws_l[row0 + s];
+    const int d = threadIdx.x, lane = d & 31;
+    const int J = p.H * p.head_groups;
+    const int kvh = qh / p.G, hl = qh % p.G;
+    const int item = kvh * p.head_groups + hl / kHeadsPerCta, h = hl % kHeadsPerCta;
+    const int pre = __ldg(p.tile_prefix + seq), n_s = __ldg(p.tile_prefix + seq + 1) - pre;
+    const int64_t total = __ldg(p.tile_prefix + p.num_seqs);
+    const int64_t ng = p.stream_groups;
+    float acc = 0.0f;
+    float l_all = 0.0f;
+    if (n_s > 0) {                                                     // uniform for the CTA
+        const int64_t a = pre, b = a + n_s;                            // the sequence's tiles
+        const int64_t g_first = ((a + 1) * ng - 1) / total;           // group holding tile a
+        const int64_t g_last = (b * ng - 1) / total;                  // group holding tile b - 1
+        float m_all = -INFINITY;
+        for (int64_t g0 = g_first; g0 <= g_last; g0 += 32) {           // normally one round
+            const int64_t gi = g0 + lane;
+            // groups whose piece is empty (more groups than tiles) wrote nothing
+            const bool live = gi <= g_last && gi * total / ng < (gi + 1) * total / ng;
+            const int64_t r = ((gi + seq) * J + item) * kHeadsPerCta + h;
+            if (d < 32) {
+                const float m = live ? p.ws_m[r] : -INFINITY;
+                const float l = live ? p.ws_l[r] : 0.0f;
+                float m_round = m;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m_round = fmaxf(m_round, __shfl_xor_sync(0xffffffffu, m_round, o));
+                const float m_new = fmaxf(m_all, m_round);
+                const float w = live ? exp2f(m - m_new) : 0.0f;
+                float l_round = w * l;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) l_round += __shfl_xor_sync(0xffffffffu, l_round, o);
+                w_s[lane] = w;
+                if (lane == 0) { m_s = m_new; l_s = l_round; }
+            }
+            __syncthreads();
+            const float rescale = exp2f(m_all - m_s);                  // 0 in the first round
+            acc *= rescale;
+            l_all = l_all * rescale + l_s;
+            m_all = m_s;
+            const int64_t left = g_last - g0 + 1;
+            const int n_here = left < 32 ? static_cast<int>(left) : 32;
+            for (int k = 0; k < n_here; ++k) {
+                const float w = w_s[k];
+                if (w != 0.0f) acc += w * p.ws_o[(((g0 + k + seq) * J + item) * kHeadsPerCta + h) * kHeadDim + d];
+            }
+            __syncthreads();
+        }
     }
-    // an empty sequence yields zeros (the reference starts l at 1 and acc at 0)
-    const float o = n_act > 0 ? acc / l_all : 0.0f;
+    const float o = n_s > 0 ? acc / l_all : 0.0f;      // an empty sequence yields zeros
     o_s[d] = round_to<T>(o);
     __syncthreads();
     // out[j] = sum_k o[k] R[k][j] over the 4x4 block of j, ascending k, fused multiply-adds
-    const int b = d & ~3;
-    float r = __fmul_rn(o_s[b], __ldg(p.rotation + b * kHeadDim + d));
+    const int b4 = d & ~3;
+    float r = __fmul_rn(o_s[b4], __ldg(p.rotation + b4 * kHeadDim + d));
 #pragma unroll
-    for (int k = 1; k < 4; ++k) r = __fmaf_rn(o_s[b + k], __ldg(p.rotation + (b + k) * kHeadDim + d), r);
+    for (int k = 1; k < 4; ++k) r = __fmaf_rn(o_s[b4 + k], __ldg(p.rotation + (b4 + k) * kHeadDim + d), r);
     T* dst = static_cast<T*>(p.out) + seq * p.o_stride_seq + static_cast<int64_t>(qh) * p.o_stride_head + d;
     store_rounded(dst, r);
 }
 
 // ---- host side -------------------------------------------------------------------------------
 
-struct SplitPlan {
-    int tiles_per_split;
-    int num_splits;
+// Grid of the streaming kernel and the scratch it needs.  Warps get at least 8 tiles each when
+// the bound on the work allows; the grid never exceeds two 8-warp CTAs per SM (148 SMs).
+struct StreamPlan {
+    int warps;             // launched warps (multiple of 8)
+    int groups;            // groups of J warps
+    size_t rows;           // partial-result rows: (group + sequence) * J + item
+    size_t prefix_bytes;
+    size_t bytes;
 };
-
-// Context splits: enough CTAs for two full waves (148 SMs x 2 CTAs) when the batch alone does
-// not provide them, at least 16 tiles (256 tokens) and at most 128 tiles (2048 tokens) per split.
-static SplitPlan plan_splits(int num_seqs, int H, int head_groups, int max_seq_len, int forced) {
-    const int max_tiles = max_seq_len > 0 ? (max_seq_len + kTile - 1) / kTile : 1;
-    int splits;
-    if (forced > 0) {
-        splits = forced;
-    } else {
-        const long long base = 1LL * num_seqs * H * head_groups;
-        const long long want = 2LL * 148 * 2;
-        splits = static_cast<int>((want + base - 1) / base);
-        const int by_min = (max_tiles + 15) / 16;       // >= 16 tiles per split
-        const int by_max = (max_tiles + 127) / 128;     // <= 128 tiles per split
-        if (splits > by_min) splits = by_min;
-        if (splits < by_max) splits = by_max;
-        if (splits < 1) splits = 1;
-    }
-    if (splits > max_tiles) splits = max_tiles;
-    SplitPlan pl;
-    pl.tiles_per_split = (max_tiles + splits - 1) / splits;
-    pl.num_splits = (max_tiles + pl.tiles_per_split - 1) / pl.tiles_per_split;
+// Groups get at least 8 tiles each when the bound on the work allows; the grid never exceeds two
+// 8-warp CTAs per SM (148 SMs).  `forced` > 0 asks for that many pieces per sequence.
+static StreamPlan plan_stream(int num_seqs, int H, int head_groups, int max_seq_len, int forced) {
+    const long long J = 1LL * H * head_groups;
+    const long long max_tiles = max_seq_len > 0 ? (max_seq_len + kTile - 1) / kTile : 1;
+    const long long work = 1LL * num_seqs * max_tiles;                   // tiles per item, at most
+    long long groups = forced > 0 ? 1LL * forced * num_seqs : (work + 7) / 8;
+    long long cap = (forced > 0 ? 4LL : 1LL) * 148 * 2 * kDecodeWarps / J;
+    if (cap < 1) cap = 1;
+    if (groups > cap) groups = cap;
+    if (groups < 1) groups = 1;
+    StreamPlan pl;
+    pl.groups = static_cast<int>(groups);
+    pl.warps = static_cast<int>((groups * J + kDecodeWarps - 1) / kDecodeWarps * kDecodeWarps);
+    pl.rows = static_cast<size_t>((groups + num_seqs) * J);
+    pl.prefix_bytes = (static_cast<size_t>(num_seqs + 1) * sizeof(int32_t) + 255) / 256 * 256;
+    pl.bytes = pl.prefix_bytes + pl.rows * kHeadsPerCta * (kHeadDim + 2) * sizeof(float);
     return pl;
-}
-
-static size_t workspace_bytes_for(int num_seqs, int Hq, int splits) {
-    const size_t rows = static_cast<size_t>(num_seqs) * Hq * splits;
-    return rows * (kHeadDim + 2) * sizeof(float);
 }
 
 template <typename T, int KB, int VB>
 static int launch_decode(const DecodeParams& p, int num_seqs, cudaStream_t st) {
-    const size_t smem = sizeof(DecodeSmem);
-    if (int e = ensure_smem(decode_split_kernel<T, KB, VB>, smem)) return e;
-    dim3 grid(p.num_splits, p.H * p.head_groups, num_seqs);
-    decode_split_kernel<T, KB, VB><<<grid, kDecodeThreads, smem, st>>>(p);
-    if (int e = check_cuda(cudaGetLastError(), "rq_decode split launch")) return e;
-    decode_merge_kernel<T><<<num_seqs * p.Hq, kHeadDim, 0, st>>>(p);
+    const size_t smem = kDecodeWarps * sizeof(StreamWarpSmem);
+    if (int e = ensure_smem(decode_stream_kernel<T, KB, VB>, smem)) return e;
+    decode_plan_kernel<<<1, 1024, 0, st>>>(p.seq_lens, num_seqs, const_cast<int32_t*>(p.tile_prefix));
+    if (int e = check_cuda(cudaGetLastError(), "rq_decode plan launch")) return e;
+    decode_stream_kernel<T, KB, VB><<<p.stream_warps / kDecodeWarps, kDecodeThreads, smem, st>>>(p);
+    if (int e = check_cuda(cudaGetLastError(), "rq_decode stream launch")) return e;
+    decode_stream_merge_kernel<T><<<num_seqs * p.Hq, kHeadDim, 0, st>>>(p);
     return check_cuda(cudaGetLastError(), "rq_decode merge launch");
 }
 
@@ -787,8 +842,7 @@ extern "C" size_t rq_decode_workspace_bytes(int num_seqs, int num_q_heads, int n
     if (num_seqs <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim != kHeadDim) return 0;
     const int G = num_q_heads / num_kv_heads;
     const int head_groups = (G + kHeadsPerCta - 1) / kHeadsPerCta;
-    const SplitPlan pl = plan_splits(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits);
-    return workspace_bytes_for(num_seqs, num_q_heads, pl.num_splits);
+    return plan_stream(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits).bytes;
 }
 
 extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq,
@@ -827,8 +881,8 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
 
     const int G = num_q_heads / num_kv_heads;
     const int head_groups = (G + kHeadsPerCta - 1) / kHeadsPerCta;
-    const SplitPlan pl = plan_splits(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits);
-    const size_t need = workspace_bytes_for(num_seqs, num_q_heads, pl.num_splits);
+    const StreamPlan pl = plan_stream(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits);
+    const size_t need = pl.bytes;
     if (!workspace || workspace_bytes < need)
         return fail(RQ_ERR_WORKSPACE, "rq_decode: workspace of %zu bytes needed, %zu given", need,
                     workspace_bytes);
@@ -844,11 +898,15 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
     p.seq_lens = seq_lens; p.cent_k = centroids_k; p.cent_v = centroids_v; p.rotation = rotation;
     p.qk_scale = sm_scale * 1.4426950408889634f;
     p.H = num_kv_heads; p.Hq = num_q_heads; p.G = G; p.head_groups = head_groups;
-    p.tiles_per_split = pl.tiles_per_split; p.num_splits = pl.num_splits;
-    const size_t rows = static_cast<size_t>(num_seqs) * num_q_heads * pl.num_splits;
-    p.ws_o = static_cast<float*>(workspace);
+    p.tile_prefix = static_cast<const int32_t*>(workspace);
+    const size_t rows = pl.rows * kHeadsPerCta;
+    p.ws_o = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.prefix_bytes);
     p.ws_m = p.ws_o + rows * kHeadDim;
     p.ws_l = p.ws_m + rows;
+    p.num_seqs = num_seqs; p.stream_warps = pl.warps; p.stream_groups = pl.groups;
+    p.bs_shift = -1;
+    for (int sft = 0; sft < 31; ++sft)
+        if ((1 << sft) == block_size) p.bs_shift = sft;
     p.out = out; p.o_stride_seq = o_stride_seq; p.o_stride_head = o_stride_head;
 
     const int kb = n_centroids_k == 8 ? 3 : 4, vb = n_centroids_v == 8 ? 3 : 4;

@@ -62,7 +62,8 @@ def test_bad_arguments_are_rejected_without_a_device():
         _lib.check(st)
     # zero work is fine
     assert L.rq_compress(None, 2, 0, 128, 128, None, None, 7, None, None, None) == 0
-    assert L.rq_decode_workspace_bytes(4, 32, 8, 128, 2048, 1) == 4 * 32 * 1 * 130 * 4
+    # forced: one piece per sequence -> 4 groups of 8 warps; rows = (groups + sequences) * 8 items, 8 heads each
+    assert L.rq_decode_workspace_bytes(4, 32, 8, 128, 2048, 1) == 256 + (4 + 4) * 8 * 8 * 130 * 4
 
 
 def test_launchers_refuse_cpu_tensors():
