@@ -331,7 +331,7 @@ class GpuJob:
             self.gathered = torch.empty(B, w.num_q_heads, w.head_dim, dtype=w.dtype, device=device)
         torch.cuda.synchronize(device)
 
-    # one step on device-resident inputs: 3 kernel launches (compress+store, decode split, merge)
+    # one step on device-resident inputs: 4 kernel launches (compress+store, decode plan, stream, merge)
     def step(self):
         w = self.w
         self.rq.compress_and_store(self.new_k, self.new_v, self.cache, self.new_slots, self.R,
@@ -464,8 +464,8 @@ def run_gpu_arm(args, w: syn.Workload) -> None:
             "clocks": clocks, "cuda_graph": graph is not None,
             "e2e": {"value": seqs_per_step / (e2e_ms / args.steps * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": 3 * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "decode_split_kernel (+ decode_merge_kernel)",
+            "gpu_launches": 4 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "decode_stream_kernel (+ plan and merge kernels)",
                          "achieved": achieved, "peak": peak, "peak_kind": f"{peak_kind} copy bandwidth",
                          "unit": "GB/s", "frac": achieved / peak,
                          "algorithmic_bytes": alg, "kernel_ms": decode_ms,
