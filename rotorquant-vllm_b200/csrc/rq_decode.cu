@@ -22,16 +22,30 @@
 // mma.sync m16n8k16 is used on purpose: M is the 4..8 query heads of one KV head, far below the
 // 128-row tiles tcgen05 needs, and the kernel is bound by HBM bytes and dequantisation
 // instructions, not by tensor throughput.
+#include <cuda.h>          // CUtensorMap (types only; the encoder is looked up at run time)
+
+#include <cstdlib>
 #include <mutex>
+#include <string>
 
 #include "rq_common.cuh"
+#include "rq_tcgen05.cuh"
 
 namespace rq {
 
-constexpr int kDecodeWarps = 8;
+#ifndef RQ_X_WARPS
+#define RQ_X_WARPS 8
+#endif
+#ifndef RQ_X_STAGES
+#define RQ_X_STAGES 3
+#endif
+#ifndef RQ_X_VFIRST
+#define RQ_X_VFIRST 0
+#endif
+constexpr int kDecodeWarps = RQ_X_WARPS;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kTile = 16;                 // tokens per tile (one mma k-step of P@V)
-constexpr int kStages = 3;                // cp.async ring depth per warp
+constexpr int kStages = RQ_X_STAGES;                // cp.async ring depth per warp
 constexpr int kVPitch = 80;               // bytes per token row of V indices in smem (64 + pad)
 constexpr int kHeadsPerCta = 8;           // query heads handled per CTA (mma N of P@V)
 
@@ -270,6 +284,33 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Same with a zero accumulator input: starts a chain without clearing registers first.
+__device__ __forceinline__ void mma_s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// Arrive on an mbarrier and announce `bytes` of asynchronous copies that will complete on it.
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar_addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes)
+                 : "memory");
+}
+
+// TMA: copy one 2-D box (inner coordinate x in elements, outer coordinate y) of the tensor described
+// by `map` into shared memory; completion is signalled on the mbarrier.  No multicast.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y),
+        "r"(bar_addr)
+        : "memory");
+}
+
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -288,13 +329,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
-// ---- shared memory ------------------------------------------------------------
-
-struct __align__(16) Stage {
-    uint8_t k[kTile][kHalfDim];        // K indices of 16 tokens
-    uint8_t v[kTile][kVPitch];         // V indices, padded rows (conflict-free 16-byte reads)
-    float norms[2 * kTile];            // [0..15] K norms, [16..31] V norms
-};
 // ---- the streaming kernel ---------------------------------------------------------------------
 //
 // Work is the linear space of (sequence, 16-token tile).  It is cut into equal contiguous pieces,
@@ -307,76 +341,158 @@ struct __align__(16) Stage {
 // with each other.  A piece that crosses into the next sequence yields one partial result per
 // part; part (group, sequence) of item j is stored at workspace row (group + sequence) * J + j,
 // unique because group and sequence only grow along the space.
+//
+// Each warp owns a 3-stage ring of tiles in shared memory.  Two ways to fill it:
+//   TMA   (KV heads a multiple of 4, power-of-two block size >= 16): one lane issues four
+//         cp.async.bulk.tensor boxes per tile -- 16 tokens x 64 B of K indices, the same of V
+//         indices (64-byte swizzle: conflict-free reads of dense rows), and 16 tokens x 16 B
+//         around the K norm and the V norm of the head -- completing on one mbarrier per stage.
+//         Address arithmetic per tile: one block-table entry and one slot number.
+//   cp.async (any layout): every lane copies 16-, 8- or 4-byte pieces with its own addresses.
 
-struct __align__(256) StreamWarpSmem {
+// Ring stage of the cp.async path.
+struct __align__(16) Stage {
+    uint8_t k[kTile][kHalfDim];        // K indices of 16 tokens
+    uint8_t v[kTile][kVPitch];         // V indices, padded rows (conflict-free 16-byte reads)
+    float norms[2 * kTile];            // [0..15] K norms, [16..31] V norms
+};
+
+constexpr int kNormBox = 16;           // bytes per token of a norm box (4 heads)
+constexpr uint32_t kTmaTileBytes = 2 * kTile * kHalfDim + 2 * kTile * kNormBox;
+
+template <bool TMA>
+struct StreamWarpSmem;
+
+template <>
+struct __align__(256) StreamWarpSmem<false> {
     uint16_t vt[kTile][kHeadDim];      // V transposition tile; also Q set-up scratch and output stage
     Stage stage[kStages];
     uint32_t tbl_k[kTile][8];
     uint32_t tbl_v[kTile][8];
     float k_unscale[kTile];
-    float cb[2][16];                   // K and V codebooks (per warp: no CTA-wide barrier needed)
 };
-static_assert(sizeof(StreamWarpSmem::vt) >= 2 * kHeadsPerCta * kHeadDim, "vt holds the query byte planes");
-static_assert(sizeof(StreamWarpSmem::vt) >= sizeof(float) * kHeadsPerCta * kHeadDim, "vt stages the partial output");
+
+template <>
+struct __align__(512) StreamWarpSmem<true> {
+    uint8_t v[kStages][kTile * kHalfDim];    // 64-byte swizzled: chunk c of row r at c ^ ((r >> 1) & 3)
+    uint8_t k[kStages][kTile * kHalfDim];    // same swizzle
+    uint8_t kn[kStages][kTile * kNormBox];   // K norms of heads 4*(head/4) .. +3 per token
+    uint8_t vn[kStages][kTile * kNormBox];
+    uint16_t vt[kTile][kHeadDim];
+    uint32_t tbl_k[kTile][8];
+    uint32_t tbl_v[kTile][8];
+    float k_unscale[kTile];
+    uint64_t bar[kStages];                   // "tile landed" barriers
+};
+static_assert(sizeof(StreamWarpSmem<true>::vt) >= 2 * kHeadsPerCta * kHeadDim, "vt holds the query byte planes");
+static_assert(sizeof(StreamWarpSmem<true>::vt) >= sizeof(float) * kHeadsPerCta * kHeadDim, "vt stages the partial output");
+static_assert(offsetof(StreamWarpSmem<true>, vt) % 256 == 0, "vt rows must be 256-byte aligned");
+static_assert(offsetof(StreamWarpSmem<true>, kn) % 128 == 0 && offsetof(StreamWarpSmem<true>, vn) % 128 == 0,
+              "TMA destinations are 128-byte aligned");
+
+// What one lane reads of a tile, whichever way the tile reached shared memory.
+struct TileView {
+    const uint8_t* k0;       // this lane's 16 K index bytes of token g (token g + 8: + 8 * 64)
+    const uint8_t* va;       // this lane's V index bytes 0..15 of its half row of token tv
+    const uint8_t* vb;       // bytes 16..31 of the same half row
+    float norm_k, norm_v;    // norms of token (lane & 15)
+};
 
 // One 16-token tile: tables, S = Q K^T (int8), online softmax, V transposition, O += P V.
 template <typename T, int KB, int VB>
-__device__ __forceinline__ void stream_tile(StreamWarpSmem& ws, const Stage& st, int n_valid, int lane,
-                                            int g, int tig, const uint32_t (&qa)[4][4], float q_factor,
-                                            float& m_run, float& l_run, float (&o_acc)[8][4], int tv,
-                                            int vhalf, uint32_t vt_store_base, uint32_t lm_base) {
+__device__ __forceinline__ void stream_tile(uint32_t (*tbl_k)[8], uint32_t (*tbl_v)[8],
+                                            float* k_unscale, const float (&cbk)[(1 << KB) / 2],
+                                            const float (&cbv)[(1 << VB) / 2], const TileView& tvw,
+                                            int n_valid, int lane, int g, int tig,
+                                            const uint32_t (&qa)[4][4], float q_factor, float& m_run,
+                                            float& l_run, float (&o_acc)[8][4], int tv,
+                                            uint32_t vt_store_base, uint32_t lm_base) {
     // ---- per-token tables: lane builds one half (lane >> 4) of the K and of the V table of
     //      token (lane & 15), so both half-warps run the same instructions ----
     {
         const int i = lane & 15, hb = lane >> 4;
         const bool valid = i < n_valid;
-        const float norm_k = valid ? st.norms[i] : 0.0f;
-        const float norm_v = valid ? st.norms[kTile + i] : 0.0f;
+        const float norm_k = valid ? tvw.norm_k : 0.0f;
+        const float norm_v = valid ? tvw.norm_v : 0.0f;
         constexpr int NKH = (1 << KB) / 2, NVH = (1 << VB) / 2;
         float unscale;
         uint32_t lo[NKH / 4], hi[NKH / 4];
-        build_half_int_table<T, NKH>(&ws.cb[0][hb * NKH], norm_k, lo, hi, unscale);
+        build_half_int_table<T, NKH>(cbk, norm_k, lo, hi, unscale);
         uint32_t vlo[NVH / 4], vhi[NVH / 4];
-        build_half_value_table<T, NVH>(&ws.cb[1][hb * NVH], norm_v, vlo, vhi);
+        build_half_value_table<T, NVH>(cbv, norm_v, vlo, vhi);
 #pragma unroll
         for (int r = 0; r < NKH / 4; ++r) {
-            ws.tbl_k[i][hb * (NKH / 4) + r] = lo[r];
-            ws.tbl_k[i][2 * (NKH / 4) + hb * (NKH / 4) + r] = hi[r];
+            tbl_k[i][hb * (NKH / 4) + r] = lo[r];
+            tbl_k[i][2 * (NKH / 4) + hb * (NKH / 4) + r] = hi[r];
         }
 #pragma unroll
         for (int r = 0; r < NVH / 4; ++r) {
-            ws.tbl_v[i][hb * (NVH / 4) + r] = vlo[r];
-            ws.tbl_v[i][2 * (NVH / 4) + hb * (NVH / 4) + r] = vhi[r];
+            tbl_v[i][hb * (NVH / 4) + r] = vlo[r];
+            tbl_v[i][2 * (NVH / 4) + hb * (NVH / 4) + r] = vhi[r];
         }
-        if (hb == 0) ws.k_unscale[i] = unscale;
+        if (hb == 0) k_unscale[i] = unscale;
     }
     __syncwarp();
 
-    // ---- S = Q K^T on the int8 path: rows = heads (g), columns = tokens ----
-    float sc[4];
+    // ---- decompress V into the transposition buffer: lane = (token tv, half row) ----
+    auto dequant_v = [&]() {
+        const Table<VB> tb = load_table<VB>(tbl_v[tv]);
+        const uint4 va = *reinterpret_cast<const uint4*>(tvw.va);
+        const uint4 vb = *reinterpret_cast<const uint4*>(tvw.vb);
+        const uint32_t words[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-        // acc_h = [Qhi; Qlo] . Khi, acc_l = [Qhi; Qlo] . Klo: entries 0,1 are the Qhi rows,
-        // entries 2,3 the Qlo rows of the same head and the same two tokens
-        int acc_h[4] = {0, 0, 0, 0}, acc_l[4] = {0, 0, 0, 0};
-        const int tok = g + 8 * nt;
-        const uint4 kw = *reinterpret_cast<const uint4*>(&st.k[tok][16 * tig]);
-        const Table<KB> tk = load_table<KB>(ws.tbl_k[tok]);
-        const uint32_t words[4] = {kw.x, kw.y, kw.z, kw.w};
+        for (int w = 0; w < 8; ++w) {
+            uint32_t lo0, hi0, lo1, hi1;
+            lookup4<VB>(tb, words[w], lo0, hi0);
+            lookup4<VB>(tb, words[w] >> 16, lo1, hi1);
+            // chunk (8*vhalf + w) ^ (tv & 7): vt rows are 256-byte aligned, so XOR the address
+            st_shared_v4(vt_store_base ^ (16u * w), prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
+                         prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
+        }
+    };
+
+    if (RQ_X_VFIRST) dequant_v();
+
+    // ---- S = Q K^T on the int8 path: rows = heads (g), columns = tokens ----
+    // acc_h = [Qhi; Qlo] . Khi, acc_l = [Qhi; Qlo] . Klo: entries 0,1 are the Qhi rows, entries
+    // 2,3 the Qlo rows of the same head and the same two tokens.  The two token groups (nt) run
+    // as independent accumulation chains.
+    float sc[4];
+    {
+        int acc_h[2][4], acc_l[2][4];
+        uint32_t words[2][4];
+        Table<KB> tk[2];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const uint4 kw = *reinterpret_cast<const uint4*>(tvw.k0 + nt * 8 * kHalfDim);
+            words[nt][0] = kw.x; words[nt][1] = kw.y; words[nt][2] = kw.z; words[nt][3] = kw.w;
+            tk[nt] = load_table<KB>(tbl_k[g + 8 * nt]);
+        }
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            uint32_t lo0, hi0, lo1, hi1;
-            lookup4<KB>(tk, words[w], lo0, hi0);            // nibbles 0..3 -> k-slots 4tig..
-            lookup4<KB>(tk, words[w] >> 16, lo1, hi1);      // nibbles 4..7 -> k-slots 16+4tig..
-            mma_s8(acc_h, qa[w][0], qa[w][1], qa[w][2], qa[w][3], hi0, hi1);
-            mma_s8(acc_l, qa[w][0], qa[w][1], qa[w][2], qa[w][3], lo0, lo1);
-        }
-        const float2 ku = *reinterpret_cast<const float2*>(&ws.k_unscale[8 * nt + 2 * tig]);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            const int t1 = acc_h[c] * 256 + (acc_h[c + 2] + acc_l[c]);
-            const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(acc_l[c + 2]));
-            sc[2 * nt + c] = f * (q_factor * (c ? ku.y : ku.x));
+            for (int nt = 0; nt < 2; ++nt) {
+                uint32_t lo0, hi0, lo1, hi1;
+                lookup4<KB>(tk[nt], words[nt][w], lo0, hi0);            // nibbles 0..3 -> k-slots 4tig..
+                lookup4<KB>(tk[nt], words[nt][w] >> 16, lo1, hi1);      // nibbles 4..7 -> k-slots 16+4tig..
+                if (w == 0) {
+                    mma_s8_first(acc_h[nt], qa[w][0], qa[w][1], qa[w][2], qa[w][3], hi0, hi1);
+                    mma_s8_first(acc_l[nt], qa[w][0], qa[w][1], qa[w][2], qa[w][3], lo0, lo1);
+                } else {
+                    mma_s8(acc_h[nt], qa[w][0], qa[w][1], qa[w][2], qa[w][3], hi0, hi1);
+                    mma_s8(acc_l[nt], qa[w][0], qa[w][1], qa[w][2], qa[w][3], lo0, lo1);
+                }
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const float2 ku = *reinterpret_cast<const float2*>(&k_unscale[8 * nt + 2 * tig]);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int t1 = acc_h[nt][c] * 256 + (acc_h[nt][c + 2] + acc_l[nt][c]);
+                const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(acc_l[nt][c + 2]));
+                sc[2 * nt + c] = f * (q_factor * (c ? ku.y : ku.x));
+            }
         }
     }
     if (n_valid < kTile) {
@@ -421,22 +537,7 @@ __device__ __forceinline__ void stream_tile(StreamWarpSmem& ws, const Stage& st,
     const uint32_t pl0 = pack_pair<T>(pr[0] - h0.x, pr[1] - h0.y);
     const uint32_t pl1 = pack_pair<T>(pr[2] - h1.x, pr[3] - h1.y);
 
-    // ---- decompress V into the transposition buffer: lane = (token tv, half row) ----
-    {
-        const Table<VB> tb = load_table<VB>(ws.tbl_v[tv]);
-        const uint4 va = *reinterpret_cast<const uint4*>(&st.v[tv][32 * vhalf]);
-        const uint4 vb = *reinterpret_cast<const uint4*>(&st.v[tv][32 * vhalf + 16]);
-        const uint32_t words[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-#pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            uint32_t lo0, hi0, lo1, hi1;
-            lookup4<VB>(tb, words[w], lo0, hi0);
-            lookup4<VB>(tb, words[w] >> 16, lo1, hi1);
-            // chunk (8*vhalf + w) ^ (tv & 7): vt rows are 256-byte aligned, so XOR the address
-            st_shared_v4(vt_store_base ^ (16u * w), prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
-                         prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
-        }
-    }
+    if (!RQ_X_VFIRST) dequant_v();
     __syncwarp();
 
     // ---- O^T += V^T P^T : rows = 16 head-dim positions per m-tile, columns = heads ----
@@ -449,8 +550,8 @@ __device__ __forceinline__ void stream_tile(StreamWarpSmem& ws, const Stage& st,
     }
 }
 
-// Tiles of every sequence as an exclusive prefix sum: prefix[s] = sum_{s' < s} ceil(len[s'] / 16).
-__global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num_seqs,
+// Tiles of every sequence as an exclusive prefix sum: prefix[s] = sum_{s' < s} ceil(len[s'] / tile_tokens).
+__global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num_seqs, int tile_tokens,
                                    int32_t* __restrict__ prefix) {
     __shared__ int warp_sums[32];
     __shared__ int carry;
@@ -458,7 +559,7 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num
     __syncthreads();
     for (int base = 0; base < num_seqs; base += blockDim.x) {
         const int s = base + threadIdx.x;
-        const int n = s < num_seqs ? (max(__ldg(seq_lens + s), 0) + kTile - 1) / kTile : 0;
+        const int n = s < num_seqs ? (max(__ldg(seq_lens + s), 0) + tile_tokens - 1) / tile_tokens : 0;
         int incl = n;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -477,12 +578,16 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num
     if (threadIdx.x == 0) prefix[num_seqs] = carry;
 }
 
-template <typename T, int KB, int VB>
+template <typename T, int KB, int VB, bool TMA>
 __global__ void __launch_bounds__(kDecodeThreads, 2)
-decode_stream_kernel(const DecodeParams p) {
-    extern __shared__ __align__(256) uint8_t smem_raw[];
+decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_idx,
+                     const __grid_constant__ CUtensorMap map_norm) {
+    extern __shared__ uint8_t smem_raw[];
+    using Smem = StreamWarpSmem<TMA>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    StreamWarpSmem& ws = reinterpret_cast<StreamWarpSmem*>(smem_raw)[warp];
+    // the dynamic area is aligned by hand: swizzled TMA tiles want 512-byte alignment
+    uint8_t* smem_base = smem_raw + ((512u - (smem_u32(smem_raw) & 511u)) & 511u);
+    Smem& ws = reinterpret_cast<Smem*>(smem_base)[warp];
     const int g = lane >> 2, tig = lane & 3;
 
     // ---- this warp's piece: warp = (group, item); a group of J consecutive warps walks one
@@ -497,11 +602,14 @@ decode_stream_kernel(const DecodeParams p) {
     const int64_t x_end = (group + 1) * total / p.stream_groups;
     if (x >= x_end) return;
 
-    if (lane < 32) {
-        const int kv = lane >> 4, i = lane & 15;
-        const int n = kv ? (1 << VB) : (1 << KB);
-        ws.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
-    }
+    // this lane's half of the codebooks (the half-table it builds for every token)
+    constexpr int NKH = (1 << KB) / 2, NVH = (1 << VB) / 2;
+    float cbk[NKH], cbv[NVH];
+#pragma unroll
+    for (int i = 0; i < NKH; ++i) cbk[i] = __ldg(p.cent_k + (lane >> 4) * NKH + i);
+#pragma unroll
+    for (int i = 0; i < NVH; ++i) cbv[i] = __ldg(p.cent_v + (lane >> 4) * NVH + i);
+
     const SlotLayout lay = slot_layout(p.H);
     const bool fast_bt = p.bs_shift >= 4;                      // power-of-two block size >= 16
     const int v_align = (lay.v_idx % 16 == 0) ? 16 : ((lay.v_idx % 8 == 0) ? 8 : 4);
@@ -511,6 +619,18 @@ decode_stream_kernel(const DecodeParams p) {
     const int lm_chunk = (lane >> 3) & 1;
     const uint32_t vt_store_base = smem_u32(&ws.vt[tv][0]) + 128u * vhalf + 16u * (tv & 7);
     const uint32_t lm_base = smem_u32(&ws.vt[lm_tok][0]) + 16u * (lm_chunk ^ (lm_tok & 7));
+
+    uint32_t par_bits = 0;                                     // TMA: phase parity of each stage barrier
+    bool dead = false;                                         // TMA: a bounded wait expired
+    if constexpr (TMA) {
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) mbar_init(&ws.bar[s], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+    }
 
     // sequence holding position x: first s with prefix[s + 1] > x
     int seq = 0;
@@ -535,81 +655,114 @@ decode_stream_kernel(const DecodeParams p) {
         const int seq_len = max(__ldg(p.seq_lens + seq), 0);
         const int32_t* bt_row = p.block_table + seq * p.bt_stride;
 
-        auto clamp_block = [&](int64_t blk) -> int64_t {
-            return blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
+        // ---- ring filling ----
+        int pf_tile = t_begin, pf_stage = 0;
+        [[maybe_unused]] int pf_blk = 0;                           // TMA: block of tile pf_tile
+        [[maybe_unused]] const uint8_t* pf_base = nullptr;         // cp.async: first slot of tile pf_tile
+        const int last_blk = static_cast<int>(p.num_blocks) - 1;
+        auto block_of = [&](int tile) -> int {                     // fast paths: block holding the tile
+            const int blk = __ldg(bt_row + ((tile * kTile) >> p.bs_shift));
+            return blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
         };
-        auto tile_base = [&](int tile) -> const uint8_t* {     // fast path: first slot of the tile
-            const int t0 = tile * kTile;
-            const int64_t blk = clamp_block(__ldg(bt_row + (t0 >> p.bs_shift)));
-            return p.cache + ((blk << p.bs_shift) + (t0 & (p.block_size - 1))) * p.total_bytes;
-        };
-        auto token_ptr = [&](int tile, int i) -> const uint8_t* {   // general path
-            const int t = min(tile * kTile + i, seq_len - 1);
-            const int64_t blk = clamp_block(__ldg(bt_row + t / p.block_size));
-            return p.cache + (blk * p.block_size + (t % p.block_size)) * p.total_bytes;
-        };
-        const uint32_t src_k = (lane >> 2) * tb + kvh * kHalfDim + 16 * (lane & 3);
-        const uint32_t dst_k = (lane >> 2) * kHalfDim + 16 * (lane & 3);
-        const uint32_t dst_v16 = sizeof(Stage::k) + (lane >> 2) * kVPitch + 16 * (lane & 3);
-        const uint32_t src_n = (lane & 15) * tb + ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh;
-        const uint32_t dst_n = sizeof(Stage::k) + sizeof(Stage::v) + 4 * lane;
-        auto issue = [&](int tile, int s, const uint8_t* base) {
-            uint8_t* stg = reinterpret_cast<uint8_t*>(&ws.stage[s]);
-            if (fast_bt) {
-                cp_async16(stg + dst_k, base + src_k);
-                cp_async16(stg + dst_k + 8 * kHalfDim, base + src_k + 8 * tb);
-                if (v_align == 16) {
-                    cp_async16(stg + dst_v16, base + src_k + lay.v_idx);
-                    cp_async16(stg + dst_v16 + 8 * kVPitch, base + src_k + 8 * tb + lay.v_idx);
-                } else if (v_align == 8) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int c = lane + 32 * j, i = c >> 3, part = c & 7;
-                        cp_async8(stg + sizeof(Stage::k) + i * kVPitch + 8 * part,
-                                  base + i * tb + lay.v_idx + kvh * kHalfDim + 8 * part);
+        // cp.async path: per-lane source and destination offsets
+        [[maybe_unused]] const uint32_t src_k = (lane >> 2) * tb + kvh * kHalfDim + 16 * (lane & 3);
+        [[maybe_unused]] const uint32_t dst_k = (lane >> 2) * kHalfDim + 16 * (lane & 3);
+        [[maybe_unused]] const uint32_t dst_v16 = sizeof(Stage::k) + (lane >> 2) * kVPitch + 16 * (lane & 3);
+        [[maybe_unused]] const uint32_t src_n = (lane & 15) * tb + ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh;
+        [[maybe_unused]] const uint32_t dst_n = sizeof(Stage::k) + sizeof(Stage::v) + 4 * lane;
+        // TMA path: byte coordinates of the four boxes inside a slot
+        [[maybe_unused]] const int x_k = kvh * kHalfDim, x_v = lay.v_idx + kvh * kHalfDim;
+        [[maybe_unused]] const int x_kn = lay.k_norm + kNormBox * (kvh >> 2);
+        [[maybe_unused]] const int x_vn = lay.v_norm + kNormBox * (kvh >> 2);
+
+        auto issue_next = [&]() {
+            if constexpr (TMA) {
+                if (pf_tile < t_end) {
+                    const int slot = (pf_blk << p.bs_shift) + ((pf_tile * kTile) & (p.block_size - 1));
+                    if (lane == 0) {
+                        const uint32_t bar = smem_u32(&ws.bar[0]) + 8u * pf_stage;
+                        mbar_expect_tx(bar, kTmaTileBytes);
+                        tma_load_2d(smem_u32(&ws.k[0][0]) + 1024u * pf_stage, &map_idx, x_k, slot, bar);
+                        tma_load_2d(smem_u32(&ws.kn[0][0]) + 256u * pf_stage, &map_norm, x_kn, slot, bar);
+                        tma_load_2d(smem_u32(&ws.vn[0][0]) + 256u * pf_stage, &map_norm, x_vn, slot, bar);
+                        tma_load_2d(smem_u32(&ws.v[0][0]) + 1024u * pf_stage, &map_idx, x_v, slot, bar);
                     }
-                } else {
+                    ++pf_tile;
+                    pf_stage = pf_stage + 1 == kStages ? 0 : pf_stage + 1;
+                    if (pf_tile < t_end) pf_blk = block_of(pf_tile);
+                }
+            } else {
+                if (pf_tile < t_end) {
+                    uint8_t* stg = reinterpret_cast<uint8_t*>(&ws.stage[pf_stage]);
+                    if (fast_bt) {
+                        const uint8_t* base = pf_base;
+                        cp_async16(stg + dst_k, base + src_k);
+                        cp_async16(stg + dst_k + 8 * kHalfDim, base + src_k + 8 * tb);
+                        if (v_align == 16) {
+                            cp_async16(stg + dst_v16, base + src_k + lay.v_idx);
+                            cp_async16(stg + dst_v16 + 8 * kVPitch, base + src_k + 8 * tb + lay.v_idx);
+                        } else if (v_align == 8) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int c = lane + 32 * j, i = c >> 4, part = c & 15;
-                        cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
-                                  base + i * tb + lay.v_idx + kvh * kHalfDim + 4 * part);
+                            for (int j = 0; j < 4; ++j) {
+                                const int c = lane + 32 * j, i = c >> 3, part = c & 7;
+                                cp_async8(stg + sizeof(Stage::k) + i * kVPitch + 8 * part,
+                                          base + i * tb + lay.v_idx + kvh * kHalfDim + 8 * part);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int c = lane + 32 * j, i = c >> 4, part = c & 15;
+                                cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
+                                          base + i * tb + lay.v_idx + kvh * kHalfDim + 4 * part);
+                            }
+                        }
+                        cp_async4(stg + dst_n, base + src_n);
+                    } else {
+                        auto token_ptr = [&](int i) -> const uint8_t* {
+                            const int t = min(pf_tile * kTile + i, seq_len - 1);
+                            int64_t blk = __ldg(bt_row + t / p.block_size);
+                            blk = blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
+                            return p.cache + (blk * p.block_size + (t % p.block_size)) * p.total_bytes;
+                        };
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const int c = lane + 32 * j, i = c >> 2, part = c & 3;
+                            cp_async16(stg + i * kHalfDim + 16 * part,
+                                       token_ptr(i) + lay.k_idx + kvh * kHalfDim + 16 * part);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int c = lane + 32 * j, i = c >> 4, part = c & 15;
+                            cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
+                                      token_ptr(i) + lay.v_idx + kvh * kHalfDim + 4 * part);
+                        }
+                        cp_async4(stg + dst_n, token_ptr(lane & 15) +
+                                                   ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh);
+                    }
+                    ++pf_tile;
+                    pf_stage = pf_stage + 1 == kStages ? 0 : pf_stage + 1;
+                    if (fast_bt && pf_tile < t_end) {
+                        const int64_t slot = (static_cast<int64_t>(block_of(pf_tile)) << p.bs_shift) +
+                                             ((pf_tile * kTile) & (p.block_size - 1));
+                        pf_base = p.cache + slot * p.total_bytes;
                     }
                 }
-                cp_async4(stg + dst_n, base + src_n);
-                return;
+                cp_async_commit();
             }
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int c = lane + 32 * j, i = c >> 2, part = c & 3;
-                cp_async16(stg + i * kHalfDim + 16 * part,
-                           token_ptr(tile, i) + lay.k_idx + kvh * kHalfDim + 16 * part);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int c = lane + 32 * j, i = c >> 4, part = c & 15;
-                cp_async4(stg + sizeof(Stage::k) + i * kVPitch + 4 * part,
-                          token_ptr(tile, i) + lay.v_idx + kvh * kHalfDim + 4 * part);
-            }
-            cp_async4(stg + dst_n, token_ptr(tile, lane & 15) +
-                                       ((lane >> 4) ? lay.v_norm : lay.k_norm) + 4 * kvh);
         };
-
         // first tiles in flight before the query set-up; the block-table entry of the tile after
         // the one being issued is read one step ahead so that its latency is off the issue path
-        int pf_tile = t_begin, pf_stage = 0;
-        const uint8_t* pf_base = fast_bt ? tile_base(t_begin) : nullptr;
-        auto issue_next = [&]() {
-            if (pf_tile < t_end) {
-                issue(pf_tile, pf_stage, pf_base);
-                ++pf_tile;
-                pf_stage = pf_stage + 1 == kStages ? 0 : pf_stage + 1;
-                if (fast_bt && pf_tile < t_end) pf_base = tile_base(pf_tile);
-            }
-            cp_async_commit();
-        };
+        if constexpr (TMA) {
+            pf_blk = block_of(t_begin);
+        } else if (fast_bt) {
+            const int64_t slot = (static_cast<int64_t>(block_of(t_begin)) << p.bs_shift) +
+                                 ((t_begin * kTile) & (p.block_size - 1));
+            pf_base = p.cache + slot * p.total_bytes;
+        }
+        if (!dead) {
 #pragma unroll 1
-        for (int s = 0; s < kStages - 1; ++s) issue_next();
+            for (int s = 0; s < kStages - 1; ++s) issue_next();
+        }
 
         // ---- queries of this item: rotate, round, quantise to signed byte planes (scratch: vt) ----
         uint8_t* q_hi = reinterpret_cast<uint8_t*>(&ws.vt[0][0]);     // [8][128]
@@ -668,19 +821,54 @@ decode_stream_kernel(const DecodeParams p) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) o_acc[mt][c] = 0.0f;
 
+        // this lane's read offsets inside a stage
+        [[maybe_unused]] const int sw_k = (g >> 1) & 3, sw_v = (tv >> 1) & 3;
+        [[maybe_unused]] const uint32_t tk_off = g * kHalfDim + 16 * (tig ^ sw_k);
+        [[maybe_unused]] const uint32_t tva_off = tv * kHalfDim + 16 * ((2 * vhalf) ^ sw_v);
+        [[maybe_unused]] const uint32_t tn_off = kNormBox * (lane & 15) + 4 * (kvh & 3);
+
         int cur_stage = 0;
 #pragma unroll 1
-        for (int tile = t_begin; tile < t_end; ++tile) {
+        for (int tile = t_begin; tile < t_end && !dead; ++tile) {
             issue_next();
-            cp_async_wait<kStages - 1>();
-            __syncwarp();
-            const Stage& st = ws.stage[cur_stage];
+            TileView view;
+            if constexpr (TMA) {
+                if (!mbar_wait(&ws.bar[cur_stage], (par_bits >> cur_stage) & 1u)) {
+                    // A copy that never landed: give the tiles in flight one more bounded wait
+                    // each and stop streaming; this and all later parts of the warp are marked
+                    // invalid (NaN row sum), which the merge turns into NaN outputs.
+#pragma unroll 1
+                    for (int s = 0; s < kStages; ++s) mbar_wait(&ws.bar[s], (par_bits >> s) & 1u);
+                    dead = true;
+                    break;
+                }
+                par_bits ^= 1u << cur_stage;
+                view.k0 = ws.k[cur_stage] + tk_off;
+                view.va = ws.v[cur_stage] + tva_off;
+                view.vb = ws.v[cur_stage] + (tva_off ^ 16u);
+                view.norm_k = *reinterpret_cast<const float*>(ws.kn[cur_stage] + tn_off);
+                view.norm_v = *reinterpret_cast<const float*>(ws.vn[cur_stage] + tn_off);
+            } else {
+                cp_async_wait<kStages - 1>();
+                __syncwarp();
+                const Stage& st = ws.stage[cur_stage];
+                view.k0 = &st.k[g][16 * tig];
+                view.va = &st.v[tv][32 * vhalf];
+                view.vb = view.va + 16;
+                view.norm_k = st.norms[lane & 15];
+                view.norm_v = st.norms[kTile + (lane & 15)];
+            }
             cur_stage = cur_stage + 1 == kStages ? 0 : cur_stage + 1;
-            stream_tile<T, KB, VB>(ws, st, min(kTile, seq_len - tile * kTile), lane, g, tig, qa, q_factor,
-                                   m_run, l_run, o_acc, tv, vhalf, vt_store_base, lm_base);
+            stream_tile<T, KB, VB>(ws.tbl_k, ws.tbl_v, ws.k_unscale, cbk, cbv, view,
+                                   min(kTile, seq_len - tile * kTile), lane, g, tig, qa, q_factor,
+                                   m_run, l_run, o_acc, tv, vt_store_base, lm_base);
             __syncwarp();      // the stage, the tables and vt may be overwritten from here on
         }
-        cp_async_wait<0>();
+        if constexpr (TMA) {
+            if (dead) l_run = __int_as_float(0x7fc00000);
+        } else {
+            cp_async_wait<0>();
+        }
 
         // ---- partial result of this part -> workspace row (warp + item) ----
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -710,6 +898,503 @@ decode_stream_kernel(const DecodeParams p) {
         x += t_end - t_begin;
         if (t_end == n_s) ++seq;
     }
+}
+
+// ---- the tensor-memory kernel -------------------------------------------------------------------
+//
+// One CTA of 128 threads streams 128-token tiles of one (KV head, head group) item; thread t owns
+// token t of the tile and TMEM lane t.  Per tile:
+//   1. the thread builds the K and V tables of its token and turns the 128 K indices into the two
+//      signed digit planes of the 15-bit integer image (32 registers each), which it stores into
+//      its TMEM lane: the K tile never touches shared memory;
+//   2. S^T = K Q^T on the tcgen05 int8 path with the K planes as the TMEM A operand and the query
+//      digit planes (rows 0..7 high digits of the 8 heads, rows 8..15 low digits) as a 2 KB shared
+//      B operand: two accumulators of 16 columns (K high x [Q high | Q low], K low x [..]);
+//   3. meanwhile the thread decompresses the V row of its token into the shared V tile, in the
+//      core-matrix order of an MN-major operand (the tensor core does the transposition);
+//   4. each thread reads the 32 sums of its token, forms the G scores, exponentiates against a
+//      CTA-wide lazy reference maximum per head (it moves only when a score exceeds it by 2^8,
+//      found with one block vote), and writes its probabilities, split into hi + lo parts of T
+//      precision, as 16 values of the shared P tile;
+//   5. O^T += V^T [P hi | P lo] on the tcgen05 16-bit path: 128 head-dim lanes x 16 columns.
+// Index bytes and norms go straight from global memory into registers, one tile ahead; the four
+// 16-byte loads of a thread cover whole 32-byte sectors, which the L1 keeps between the loads.
+// Pieces, partial-result rows and the merge are those of the streaming kernel with 128-token tiles
+// and one CTA per (group, item).
+
+constexpr int kUTile = 128;                  // tokens per tile
+constexpr int kUThreads = 128;
+constexpr int kUCtasPerSm = 4;
+constexpr uint32_t kUTmemCols = 128;         // columns allocated per CTA
+constexpr uint32_t kUColKhi = 0, kUColKlo = 32, kUColS = 64, kUColO = 96;
+
+struct __align__(512) UmmaSmem {
+    uint8_t stage[4][2][32 * kHalfDim];      // per warp: K | V index rows of its 32 tokens of the next tile
+                                             // (TMA, 64-byte swizzle: chunk c of row r at c ^ ((r >> 1) & 3))
+    uint16_t v[kUTile * kHeadDim];           // V tile: core (token/8)*16 + pos/8, core row token%8
+    uint16_t p[kUTile * 16];                 // P tile: core (token/8)*2 + n/8, core row token%8
+    uint8_t q[16 * kHeadDim];                // Q digit planes, K-major: core (n/8)*8 + pos/16
+    float cb[2][16];
+    float qf[kHeadsPerCta];                  // q unscale * sm_scale * log2(e) per head
+    float red[4][kHeadsPerCta];              // cross-warp reductions
+    uint64_t bar_s, bar_o;
+    uint64_t bar_in[4];                      // per warp: "staged rows landed"
+    uint32_t tmem_base;
+};
+
+// Full tables of one token, built by one thread.
+template <typename T, int BITS>
+__device__ __forceinline__ Table<BITS> build_int_table(const float* cb, float norm, float& unscale) {
+    constexpr int N = 1 << BITS;
+    float v[N];
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        v[i] = round_to<T>(__fmul_rn(cb[i], norm));
+        mx = fmaxf(mx, fabsf(v[i]));
+    }
+    const bool ok = mx >= 1.0e-30f && mx <= 3.0e38f;
+    const int e = ok ? exponent_of(mx) : 0;
+    const float scale = ok ? pow2i(13 - e) : 0.0f;
+    unscale = ok ? pow2i(e - 13) : 0.0f;
+    Table<BITS> t;
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+        const int u0 = __float2int_rn(fmaf(v[4 * i], scale, 128.0f)), u1 = __float2int_rn(fmaf(v[4 * i + 1], scale, 128.0f));
+        const int u2 = __float2int_rn(fmaf(v[4 * i + 2], scale, 128.0f)), u3 = __float2int_rn(fmaf(v[4 * i + 3], scale, 128.0f));
+        const uint32_t a = prmt(u0, u1, 0x5140), b = prmt(u2, u3, 0x5140);
+        t.r[i] = prmt(a, b, 0x5410) ^ 0x80808080u;
+        t.r[N / 4 + i] = prmt(a, b, 0x7632);
+    }
+    return t;
+}
+template <typename T, int BITS>
+__device__ __forceinline__ Table<BITS> build_value_table(const float* cb, float norm) {
+    constexpr int N = 1 << BITS;
+    Table<BITS> t;
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+        const uint32_t p01 = pack_pair<T>(__fmul_rn(cb[4 * i], norm), __fmul_rn(cb[4 * i + 1], norm));
+        const uint32_t p23 = pack_pair<T>(__fmul_rn(cb[4 * i + 2], norm), __fmul_rn(cb[4 * i + 3], norm));
+        t.r[i] = prmt(p01, p23, 0x6420);
+        t.r[N / 4 + i] = prmt(p01, p23, 0x7531);
+    }
+    return t;
+}
+
+template <typename T, int KB, int VB, bool TMA>
+__global__ void __launch_bounds__(kUThreads, kUCtasPerSm)
+decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_idx) {
+    extern __shared__ uint8_t smem_raw[];
+    // aligned by hand: the swizzled TMA rows want 512-byte alignment
+    UmmaSmem& sm = *reinterpret_cast<UmmaSmem*>(smem_raw + ((512u - (smem_u32(smem_raw) & 511u)) & 511u));
+    constexpr int NK = 1 << KB, NV = 1 << VB;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // ---- this CTA's piece: CTA = (group, item) ----
+    const int J = p.H * p.head_groups;
+    const int64_t total = __ldg(p.tile_prefix + p.num_seqs);
+    const int64_t group = blockIdx.x / J;
+    const int item = static_cast<int>(blockIdx.x % J);
+    if (group >= p.stream_groups) return;
+    int64_t x = group * total / p.stream_groups;
+    const int64_t x_end = (group + 1) * total / p.stream_groups;
+    if (x >= x_end) return;
+
+    if (tid == 0) {
+        mbar_init(&sm.bar_s, 1);
+        mbar_init(&sm.bar_o, 1);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mbar_init(&sm.bar_in[w], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_proxy();
+    }
+    if (warp == 0) tmem_alloc(&sm.tmem_base, kUTmemCols);
+    if (tid < 32) {
+        const int kv = tid >> 4, i = tid & 15;
+        const int n = kv ? NV : NK;
+        sm.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lane quarter
+
+    const SlotLayout lay = slot_layout(p.H);
+    const int v_align = (lay.v_idx % 16 == 0) ? 16 : ((lay.v_idx % 8 == 0) ? 8 : 4);
+    // S^T: s32 accumulator, int8 operands, N = 16, M = 128;  O^T: f32 accumulator, T operands, both MN-major
+    const uint32_t idesc_s = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+    const uint32_t idesc_o = (1u << 4) | (TcFormat<T>::kFmt << 7) | (TcFormat<T>::kFmt << 10) | (1u << 15) |
+                             (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+    const uint32_t q_addr = smem_u32(sm.q), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p);
+    uint8_t* const v_dst = reinterpret_cast<uint8_t*>(sm.v) + (tid >> 3) * (16 * 128) + (tid & 7) * 16;
+    uint8_t* const p_dst = reinterpret_cast<uint8_t*>(sm.p) + (tid >> 3) * (2 * 128) + (tid & 7) * 16;
+
+    // sequence holding position x: first s with prefix[s + 1] > x
+    int seq = 0;
+    for (int base = 0; base < p.num_seqs; base += 32) {
+        const int s = base + lane;
+        const int64_t end = s < p.num_seqs ? __ldg(p.tile_prefix + s + 1) : INT64_MAX;
+        const unsigned hit = __ballot_sync(0xffffffffu, end > x);
+        if (hit) { seq = base + __ffs(hit) - 1; break; }
+    }
+
+    uint32_t ph_s = 0, ph_o = 0;              // phase parities of the two barriers
+    [[maybe_unused]] uint32_t ph_in = 0;      // ... and of this warp's staging barrier
+    bool dead = false;                        // a bounded wait expired (same value in all threads)
+    // staged rows of this thread's token: 16-byte chunk c sits at chunk c ^ ((lane >> 1) & 3)
+    [[maybe_unused]] const uint8_t* const stage_k = sm.stage[warp][0] + lane * kHalfDim;
+    [[maybe_unused]] const uint8_t* const stage_v = sm.stage[warp][1] + lane * kHalfDim;
+    [[maybe_unused]] const uint32_t stage_sw = 16u * ((lane >> 1) & 3);
+
+#pragma unroll 1
+    while (x < x_end && seq < p.num_seqs) {
+        const int pre = __ldg(p.tile_prefix + seq), n_s = __ldg(p.tile_prefix + seq + 1) - pre;
+        if (n_s <= 0 || x >= static_cast<int64_t>(pre) + n_s) { ++seq; continue; }
+        const int t_begin = static_cast<int>(x - pre);
+        const int64_t reach = t_begin + (x_end - x);
+        const int t_end = reach < n_s ? static_cast<int>(reach) : n_s;
+        const int kvh = item / p.head_groups, hg = item % p.head_groups;
+        const int heads_here = min(kHeadsPerCta, p.G - hg * kHeadsPerCta);
+        const int first_qh = kvh * p.G + hg * kHeadsPerCta;
+        const int seq_len = max(__ldg(p.seq_lens + seq), 0);
+        const int32_t* bt_row = p.block_table + seq * p.bt_stride;
+        const int last_blk = static_cast<int>(p.num_blocks) - 1;
+
+        // slot of this thread's token in a tile (nullptr past the end of the sequence)
+        auto slot_of = [&](int tile) -> const uint8_t* {
+            const int tok = tile * kUTile + tid;
+            if (tok >= seq_len) return nullptr;
+            const int bi = p.bs_shift >= 0 ? (tok >> p.bs_shift) : (tok / p.block_size);
+            const int off = p.bs_shift >= 0 ? (tok & (p.block_size - 1)) : (tok % p.block_size);
+            int blk = __ldg(bt_row + bi);
+            blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
+            return p.cache + (static_cast<int64_t>(blk) * p.block_size + off) * p.total_bytes + kvh * kHalfDim;
+        };
+        uint32_t kw[16], vw[16];
+        float nk = 0.0f, nv = 0.0f;
+        // TMA path: the warp's elected lane copies the index rows of the warp's 32 tokens of a
+        // tile (two 16-token boxes per region; a 16-token group never straddles a block) into the
+        // warp's staging rows; every call completes one phase of the warp's barrier.
+        [[maybe_unused]] auto issue_tile = [&](int tile) {
+            const int tok0 = tile * kUTile + 32 * warp;
+            int slot[2];
+            bool on[2];
+#pragma unroll
+            for (int g2 = 0; g2 < 2; ++g2) {
+                const int t = tok0 + 16 * g2;
+                on[g2] = t < seq_len;
+                int blk = on[g2] ? __ldg(bt_row + (t >> p.bs_shift)) : 0;
+                blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
+                slot[g2] = (blk << p.bs_shift) + (t & (p.block_size - 1));
+            }
+            if (lane == 0) {
+                const uint32_t bar = smem_u32(&sm.bar_in[warp]);
+                const uint32_t bytes = (on[0] ? 2048u : 0u) + (on[1] ? 2048u : 0u);
+                if (bytes != 0) {
+                    mbar_expect_tx(bar, bytes);
+#pragma unroll
+                    for (int g2 = 0; g2 < 2; ++g2) {
+                        if (on[g2]) {
+                            tma_load_2d(smem_u32(sm.stage[warp][0]) + 1024u * g2, &map_idx, kvh * kHalfDim, slot[g2], bar);
+                            tma_load_2d(smem_u32(sm.stage[warp][1]) + 1024u * g2, &map_idx, lay.v_idx + kvh * kHalfDim,
+                                        slot[g2], bar);
+                        }
+                    }
+                } else {
+                    mbar_arrive(&sm.bar_in[warp]);
+                }
+            }
+        };
+        [[maybe_unused]] auto read_stage = [&](const uint8_t* rows, uint32_t (&w)[16]) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint4 x = *reinterpret_cast<const uint4*>(rows + ((16u * c) ^ stage_sw));
+                w[4 * c] = x.x; w[4 * c + 1] = x.y; w[4 * c + 2] = x.z; w[4 * c + 3] = x.w;
+            }
+        };
+        // index words and norm of this thread's token: K (which == 0) or V (which == 1)
+        auto fetch = [&](int which, const uint8_t* slot, uint32_t (&w)[16], float& norm) {
+            if (slot != nullptr) {
+                if constexpr (TMA) {
+                    read_stage(which ? stage_v : stage_k, w);
+                } else {
+                    if (which) load_idx64(slot + lay.v_idx, v_align, w);
+                    else load_idx64(slot + lay.k_idx, 16, w);
+                }
+                norm = __ldg(reinterpret_cast<const float*>(slot + (which ? lay.v_norm : lay.k_norm) -
+                                                            kvh * (kHalfDim - 4)));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) w[i] = 0u;
+                norm = 0.0f;
+            }
+        };
+        bool failed_in = false;
+        if (!dead) {
+            const uint8_t* first = slot_of(t_begin);
+            if constexpr (TMA) {
+                issue_tile(t_begin);
+                failed_in |= !mbar_wait(&sm.bar_in[warp], ph_in);
+                ph_in ^= 1u;
+            }
+            fetch(0, first, kw, nk);
+            fetch(1, first, vw, nv);
+            if constexpr (TMA) {
+                __syncwarp();
+                if (t_begin + 1 < t_end) issue_tile(t_begin + 1);
+            }
+        }
+
+        // ---- queries of this item: rotate, round, quantise to signed digit planes (B operand) ----
+#pragma unroll 1
+        for (int round = 0; round < 2; ++round) {
+            const int h = 4 * round + warp;
+            float r[4] = {0.f, 0.f, 0.f, 0.f};
+            if (h < heads_here) {
+                const T* qp = static_cast<const T*>(p.q) + seq * p.q_stride_seq +
+                              static_cast<int64_t>(first_qh + h) * p.q_stride_head + 4 * lane;
+                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(qp));
+                const float2 x01 = unpack_pair<T>(raw.x), x23 = unpack_pair<T>(raw.y);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 rr = __ldg(reinterpret_cast<const float4*>(
+                        p.rotation + (4 * lane + j) * kHeadDim + 4 * lane));
+                    float acc = __fmul_rn(x01.x, rr.x);
+                    acc = __fmaf_rn(x01.y, rr.y, acc);
+                    acc = __fmaf_rn(x23.x, rr.z, acc);
+                    acc = __fmaf_rn(x23.y, rr.w, acc);
+                    r[j] = round_to<T>(acc);
+                }
+            }
+            float mx = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const bool ok = mx >= 1.0e-30f && mx <= 3.0e38f;
+            const int e = ok ? exponent_of(mx) : 0;
+            const float scale = ok ? pow2i(13 - e) : 0.0f;
+            int qu[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) qu[j] = __float2int_rn(fmaf(r[j], scale, 128.0f));
+            // position x of a row holds head-dim x ^ 1 (the nibble order of the cache)
+            const uint32_t a = prmt(qu[1], qu[0], 0x5140), b = prmt(qu[3], qu[2], 0x5140);
+            const uint32_t off = (lane >> 2) * 128 + (h & 7) * 16 + 4 * (lane & 3);
+            *reinterpret_cast<uint32_t*>(&sm.q[off]) = prmt(a, b, 0x7632);                       // row h: high digits
+            *reinterpret_cast<uint32_t*>(&sm.q[1024 + off]) = prmt(a, b, 0x5410) ^ 0x80808080u;  // row 8 + h: low digits
+            if (lane == 0) sm.qf[h] = (ok ? pow2i(e - 13) : 0.0f) * p.qk_scale;
+        }
+        fence_async_proxy();
+        __syncthreads();
+
+        float m_ref[kHeadsPerCta], l_acc[kHeadsPerCta];
+#pragma unroll
+        for (int h = 0; h < kHeadsPerCta; ++h) { m_ref[h] = -INFINITY; l_acc[h] = 0.0f; }
+        bool pv_pending = false;
+
+#pragma unroll 1
+        for (int tile = t_begin; tile < t_end && !dead; ++tile) {
+            const uint8_t* next_slot = tile + 1 < t_end ? slot_of(tile + 1) : nullptr;
+            const bool valid = tile * kUTile + tid < seq_len;
+            bool failed = failed_in;
+            failed_in = false;
+
+            // ---- 1, 2: K table, digit planes -> TMEM, S^T = K Q^T ----
+            float k_unscale;
+            {
+                const Table<KB> tk = build_int_table<T, KB>(sm.cb[0], nk, k_unscale);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int w = 0; w < 8; ++w) {
+                        const uint32_t word = kw[8 * half + w];
+                        lookup4<KB>(tk, word, lo[2 * w], hi[2 * w]);
+                        lookup4<KB>(tk, word >> 16, lo[2 * w + 1], hi[2 * w + 1]);
+                    }
+                    tmem_st16_nowait(lane_base + kUColKhi + 16 * half, hi);
+                    tmem_st16_nowait(lane_base + kUColKlo + 16 * half, lo);
+                }
+                tmem_wait_st();
+            }
+            if constexpr (TMA) {
+                if (tile + 1 < t_end) {                  // the staged rows of the next tile
+                    failed |= !mbar_wait(&sm.bar_in[warp], ph_in);
+                    ph_in ^= 1u;
+                }
+            }
+            fetch(0, next_slot, kw, nk);
+            tc_fence_before();
+            __syncthreads();
+            if (tid == 0) {
+                tc_fence_after();
+#pragma unroll
+                for (int s = 0; s < 4; ++s)
+                    tc_mma_i8_ta(tmem + kUColS, tmem + kUColKhi + 8 * s, smem_desc(q_addr + 256 * s, 128, 1024),
+                                 idesc_s, s > 0 ? 1u : 0u);
+#pragma unroll
+                for (int s = 0; s < 4; ++s)
+                    tc_mma_i8_ta(tmem + kUColS + 16, tmem + kUColKlo + 8 * s, smem_desc(q_addr + 256 * s, 128, 1024),
+                                 idesc_s, s > 0 ? 1u : 0u);
+                tc_commit(&sm.bar_s);
+            }
+
+            // ---- 3: V row -> shared tile (the previous tile's P V must have read it) ----
+            if (pv_pending) {
+                failed |= !mbar_wait(&sm.bar_o, ph_o);
+                ph_o ^= 1u;
+                tc_fence_after();
+            }
+            {
+                const Table<VB> tb = build_value_table<T, VB>(sm.cb[1], nv);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {       // 8 head-dims = one 32-bit index word per chunk
+                    uint32_t lo0, hi0, lo1, hi1;
+                    lookup4<VB>(tb, vw[c], lo0, hi0);
+                    lookup4<VB>(tb, vw[c] >> 16, lo1, hi1);
+                    *reinterpret_cast<uint4*>(v_dst + c * 128) =
+                        make_uint4(prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
+                                   prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
+                }
+            }
+            fetch(1, next_slot, vw, nv);
+            if constexpr (TMA) {
+                __syncwarp();                            // the staging rows are free again
+                if (tile + 2 < t_end) issue_tile(tile + 2);
+            }
+
+            // ---- 4: scores, lazy reference maximum, probabilities ----
+            failed |= !mbar_wait(&sm.bar_s, ph_s);
+            ph_s ^= 1u;
+            tc_fence_after();
+            float sc[kHeadsPerCta];
+            const float tok_bias = valid ? 0.0f : -INFINITY;
+            {
+                uint32_t d[32];
+                tmem_ld32(lane_base + kUColS, d);
+                const float4 qf0 = *reinterpret_cast<const float4*>(&sm.qf[0]);
+                const float4 qf1 = *reinterpret_cast<const float4*>(&sm.qf[4]);
+                const float qf[8] = {qf0.x, qf0.y, qf0.z, qf0.w, qf1.x, qf1.y, qf1.z, qf1.w};
+#pragma unroll
+                for (int h = 0; h < kHeadsPerCta; ++h) {
+                    // d[h] = Khi.Qhi, d[8+h] = Khi.Qlo, d[16+h] = Klo.Qhi, d[24+h] = Klo.Qlo
+                    const int t1 = static_cast<int>(d[h]) * 256 + (static_cast<int>(d[8 + h]) + static_cast<int>(d[16 + h]));
+                    const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(static_cast<int>(d[24 + h])));
+                    // heads beyond the group have factor 0: they behave like heads with all-zero scores and
+                    // their columns are never written out; tokens past the end get -inf (probability 0)
+                    sc[h] = fmaf(f, qf[h] * k_unscale, tok_bias);
+                }
+            }
+            bool grow = false;
+#pragma unroll
+            for (int h = 0; h < kHeadsPerCta; ++h) grow |= sc[h] > m_ref[h] + 8.0f;
+            if (__syncthreads_or(grow || failed)) {
+                if (__syncthreads_or(failed)) { dead = true; break; }
+                // move the reference maxima: CTA-wide maximum per head, rescale sums and O^T
+#pragma unroll
+                for (int h = 0; h < kHeadsPerCta; ++h) {
+                    float m = sc[h];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                    if (lane == 0) sm.red[warp][h] = m;
+                }
+                __syncthreads();
+                float alpha[kHeadsPerCta];
+#pragma unroll
+                for (int h = 0; h < kHeadsPerCta; ++h) {
+                    const float m_tile = fmaxf(fmaxf(sm.red[0][h], sm.red[1][h]), fmaxf(sm.red[2][h], sm.red[3][h]));
+                    const float m_new = fmaxf(m_ref[h], m_tile);
+                    alpha[h] = (m_new == -INFINITY) ? 1.0f : ex2_approx(m_ref[h] - m_new);   // 0 on the first tile
+                    l_acc[h] *= alpha[h];
+                    m_ref[h] = m_new;
+                }
+                if (tile > t_begin) {                // O^T holds a sum: lane = head-dim, column = head (hi | lo)
+                    uint32_t o[16];
+                    tmem_ld16_nowait(lane_base + kUColO, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c & 7]);
+                    tmem_st16_nowait(lane_base + kUColO, o);
+                    tmem_wait_st();
+                }
+            }
+            {
+                float pr[kHeadsPerCta];
+#pragma unroll
+                for (int h = 0; h < kHeadsPerCta; ++h) {
+                    pr[h] = ex2_approx(sc[h] - m_ref[h]);
+                    l_acc[h] += pr[h];
+                }
+                uint32_t ph[4], pl[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    ph[j] = pack_pair<T>(pr[2 * j], pr[2 * j + 1]);
+                    const float2 back = unpack_pair<T>(ph[j]);
+                    pl[j] = pack_pair<T>(pr[2 * j] - back.x, pr[2 * j + 1] - back.y);
+                }
+                *reinterpret_cast<uint4*>(p_dst) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                *reinterpret_cast<uint4*>(p_dst + 128) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+            }
+            fence_async_proxy();
+            tc_fence_before();
+            __syncthreads();
+
+            // ---- 5: O^T += V^T [P hi | P lo] ----
+            if (tid == 0) {
+                tc_fence_after();
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    tc_mma_f16(tmem + kUColO, smem_desc(v_addr + 4096 * s, 2048, 128),
+                               smem_desc(p_addr + 512 * s, 256, 128), idesc_o, (tile > t_begin || s > 0) ? 1u : 0u);
+                tc_commit(&sm.bar_o);
+            }
+            pv_pending = true;
+        }
+
+        // ---- partial result of this part -> workspace row (group + sequence) * J + item ----
+        if (pv_pending) {
+            const bool failed = !mbar_wait(&sm.bar_o, ph_o);
+            ph_o ^= 1u;
+            tc_fence_after();
+            if (__syncthreads_or(failed)) dead = true;
+        }
+#pragma unroll
+        for (int h = 0; h < kHeadsPerCta; ++h) {
+            float v = l_acc[h];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) sm.red[warp][h] = v;
+        }
+        __syncthreads();
+        const int64_t row = (group + seq) * J + item;
+        if (tid < heads_here) {
+            float m = m_ref[0];
+#pragma unroll
+            for (int h = 1; h < kHeadsPerCta; ++h) m = tid == h ? m_ref[h] : m;
+            const float l = (sm.red[0][tid] + sm.red[1][tid]) + (sm.red[2][tid] + sm.red[3][tid]);
+            p.ws_m[row * kHeadsPerCta + tid] = m;
+            p.ws_l[row * kHeadsPerCta + tid] = dead ? __int_as_float(0x7fc00000) : l;
+        }
+        if (!dead) {
+            uint32_t o[16];
+            tmem_ld16_nowait(lane_base + kUColO, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int h = 0; h < kHeadsPerCta; ++h)     // lane (position) x holds head-dim x ^ 1
+                if (h < heads_here)
+                    p.ws_o[(row * kHeadsPerCta + h) * kHeadDim + (tid ^ 1)] =
+                        __uint_as_float(o[h]) + __uint_as_float(o[8 + h]);
+        }
+        tc_fence_before();
+        __syncthreads();
+
+        x += t_end - t_begin;
+        if (t_end == n_s) ++seq;
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kUTmemCols);
 }
 
 // Merge for the streaming kernel: the parts of a (sequence, head) are the groups whose pieces
@@ -784,17 +1469,37 @@ decode_stream_merge_kernel(const DecodeParams p) {
 
 // ---- host side -------------------------------------------------------------------------------
 
-// Grid of the streaming kernel and the scratch it needs.  Warps get at least 8 tiles each when
-// the bound on the work allows; the grid never exceeds two 8-warp CTAs per SM (148 SMs).
+// Two kernels implement the decode: the tensor-memory kernel (default) and the warp-streaming
+// kernel.  RQ_DECODE_PATH=stream in the environment selects the latter (for comparisons).
+enum class DecodePath { kUmma, kStream };
+static DecodePath decode_path() {
+    static const DecodePath path = [] {
+        const char* e = std::getenv("RQ_DECODE_PATH");
+        return (e != nullptr && std::string(e) == "stream") ? DecodePath::kStream : DecodePath::kUmma;
+    }();
+    return path;
+}
+
+// Grid and scratch of one decode call.  The (sequence, tile) space is cut into `groups` equal
+// pieces; each piece is walked by J workers (warps of the streaming kernel, CTAs of the
+// tensor-memory kernel), one per (KV head, head group).
 struct StreamPlan {
-    int warps;             // launched warps (multiple of 8)
-    int groups;            // groups of J warps
+    int warps;             // streaming kernel: launched warps (multiple of 8)
+    int groups;            // pieces
     size_t rows;           // partial-result rows: (group + sequence) * J + item
     size_t prefix_bytes;
     size_t bytes;
 };
-// Groups get at least 8 tiles each when the bound on the work allows; the grid never exceeds two
-// 8-warp CTAs per SM (148 SMs).  `forced` > 0 asks for that many pieces per sequence.
+static void finish_plan(StreamPlan& pl, long long groups, long long J, int num_seqs) {
+    pl.groups = static_cast<int>(groups);
+    pl.warps = static_cast<int>((groups * J + kDecodeWarps - 1) / kDecodeWarps * kDecodeWarps);
+    pl.rows = static_cast<size_t>((groups + num_seqs) * J);
+    pl.prefix_bytes = (static_cast<size_t>(num_seqs + 1) * sizeof(int32_t) + 255) / 256 * 256;
+    pl.bytes = pl.prefix_bytes + pl.rows * kHeadsPerCta * (kHeadDim + 2) * sizeof(float);
+}
+// Streaming kernel: groups get at least 8 tiles of 16 tokens each when the bound on the work
+// allows; the grid never exceeds two 8-warp CTAs per SM (148 SMs).  `forced` > 0 asks for that
+// many pieces per sequence.
 static StreamPlan plan_stream(int num_seqs, int H, int head_groups, int max_seq_len, int forced) {
     const long long J = 1LL * H * head_groups;
     const long long max_tiles = max_seq_len > 0 ? (max_seq_len + kTile - 1) / kTile : 1;
@@ -805,22 +1510,114 @@ static StreamPlan plan_stream(int num_seqs, int H, int head_groups, int max_seq_
     if (groups > cap) groups = cap;
     if (groups < 1) groups = 1;
     StreamPlan pl;
-    pl.groups = static_cast<int>(groups);
-    pl.warps = static_cast<int>((groups * J + kDecodeWarps - 1) / kDecodeWarps * kDecodeWarps);
-    pl.rows = static_cast<size_t>((groups + num_seqs) * J);
-    pl.prefix_bytes = (static_cast<size_t>(num_seqs + 1) * sizeof(int32_t) + 255) / 256 * 256;
-    pl.bytes = pl.prefix_bytes + pl.rows * kHeadsPerCta * (kHeadDim + 2) * sizeof(float);
+    finish_plan(pl, groups, J, num_seqs);
     return pl;
+}
+// Tensor-memory kernel: one 128-token tile per piece at least; at most four CTAs per SM.
+static StreamPlan plan_umma(int num_seqs, int H, int head_groups, int max_seq_len, int forced) {
+    const long long J = 1LL * H * head_groups;
+    const long long max_tiles = max_seq_len > 0 ? (max_seq_len + kUTile - 1) / kUTile : 1;
+    const long long work = 1LL * num_seqs * max_tiles;
+    long long groups = forced > 0 ? 1LL * forced * num_seqs : work;
+    long long cap = (forced > 0 ? 4LL : 1LL) * 148 * kUCtasPerSm / J;
+    if (cap < 1) cap = 1;
+    if (groups > cap) groups = cap;
+    if (groups < 1) groups = 1;
+    StreamPlan pl;
+    finish_plan(pl, groups, J, num_seqs);
+    return pl;
+}
+static StreamPlan plan_decode(int num_seqs, int H, int head_groups, int max_seq_len, int forced) {
+    return decode_path() == DecodePath::kUmma ? plan_umma(num_seqs, H, head_groups, max_seq_len, forced)
+                                              : plan_stream(num_seqs, H, head_groups, max_seq_len, forced);
+}
+
+// ---- tensor maps of the cache for the TMA path ------------------------------------------------
+//
+// The cache is described as a 2-D byte tensor (num_slots rows of total_bytes): one map with a
+// 16 x 64 B box and 64-byte swizzle for the index regions, one with a 16 x 16 B box for the norms.
+// cuTensorMapEncodeTiled is a driver entry point; it is looked up through the runtime so that the
+// library does not link against the driver.
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+static bool encode_cache_map(CUtensorMap* map, const uint8_t* cache, int64_t num_slots, int total_bytes,
+                             int box_bytes, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(total_bytes), static_cast<cuuint64_t>(num_slots)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(total_bytes)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(kTile)};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(cache), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The TMA path needs 16-byte aligned box origins (KV heads a multiple of 4), tiles that never
+// straddle a block (power-of-two block size >= 16) and slot numbers that fit an int32 coordinate.
+// RQ_DECODE_NO_TMA=1 in the environment selects the cp.async path everywhere (for comparisons).
+static bool tma_eligible(const DecodeParams& p) {
+    static const bool disabled = [] {
+        const char* e = std::getenv("RQ_DECODE_NO_TMA");
+        return e != nullptr && e[0] != '\0' && e[0] != '0';
+    }();
+    return !disabled && p.H % 4 == 0 && p.bs_shift >= 4 && aligned(p.cache, 16) &&
+           p.num_blocks * p.block_size <= INT32_MAX && p.total_bytes == p.H * 256;
+}
+
+template <typename T, int KB, int VB, bool TMA>
+static int launch_stream(const DecodeParams& p, const CUtensorMap& map_idx, const CUtensorMap& map_norm,
+                         cudaStream_t st) {
+    const size_t smem = kDecodeWarps * sizeof(StreamWarpSmem<TMA>) + 512;    // + hand alignment
+    if (int e = ensure_smem(decode_stream_kernel<T, KB, VB, TMA>, smem)) return e;
+    decode_stream_kernel<T, KB, VB, TMA>
+        <<<p.stream_warps / kDecodeWarps, kDecodeThreads, smem, st>>>(p, map_idx, map_norm);
+    return check_cuda(cudaGetLastError(), "rq_decode stream launch");
 }
 
 template <typename T, int KB, int VB>
 static int launch_decode(const DecodeParams& p, int num_seqs, cudaStream_t st) {
-    const size_t smem = kDecodeWarps * sizeof(StreamWarpSmem);
-    if (int e = ensure_smem(decode_stream_kernel<T, KB, VB>, smem)) return e;
-    decode_plan_kernel<<<1, 1024, 0, st>>>(p.seq_lens, num_seqs, const_cast<int32_t*>(p.tile_prefix));
+    const bool umma = decode_path() == DecodePath::kUmma;
+    decode_plan_kernel<<<1, 1024, 0, st>>>(p.seq_lens, num_seqs, umma ? kUTile : kTile,
+                                           const_cast<int32_t*>(p.tile_prefix));
     if (int e = check_cuda(cudaGetLastError(), "rq_decode plan launch")) return e;
-    decode_stream_kernel<T, KB, VB><<<p.stream_warps / kDecodeWarps, kDecodeThreads, smem, st>>>(p);
-    if (int e = check_cuda(cudaGetLastError(), "rq_decode stream launch")) return e;
+    alignas(64) CUtensorMap map_idx{}, map_norm{};
+    bool tma = tma_eligible(p);
+    const int64_t num_slots = p.num_blocks * p.block_size;
+    if (tma) tma = encode_cache_map(&map_idx, p.cache, num_slots, p.total_bytes, kHalfDim, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (umma) {
+        const size_t smem = sizeof(UmmaSmem) + 512;                              // + hand alignment
+        const long long ctas = 1LL * p.stream_groups * p.H * p.head_groups;
+        if (tma) {
+            if (int e = ensure_smem(decode_umma_kernel<T, KB, VB, true>, smem)) return e;
+            decode_umma_kernel<T, KB, VB, true><<<static_cast<unsigned>(ctas), kUThreads, smem, st>>>(p, map_idx);
+        } else {
+            if (int e = ensure_smem(decode_umma_kernel<T, KB, VB, false>, smem)) return e;
+            decode_umma_kernel<T, KB, VB, false><<<static_cast<unsigned>(ctas), kUThreads, smem, st>>>(p, map_idx);
+        }
+        if (int e = check_cuda(cudaGetLastError(), "rq_decode tensor-memory launch")) return e;
+    } else {
+        if (tma) tma = encode_cache_map(&map_norm, p.cache, num_slots, p.total_bytes, kNormBox, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (int e = tma ? launch_stream<T, KB, VB, true>(p, map_idx, map_norm, st)
+                        : launch_stream<T, KB, VB, false>(p, map_idx, map_norm, st))
+            return e;
+    }
     decode_stream_merge_kernel<T><<<num_seqs * p.Hq, kHeadDim, 0, st>>>(p);
     return check_cuda(cudaGetLastError(), "rq_decode merge launch");
 }
@@ -842,7 +1639,7 @@ extern "C" size_t rq_decode_workspace_bytes(int num_seqs, int num_q_heads, int n
     if (num_seqs <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim != kHeadDim) return 0;
     const int G = num_q_heads / num_kv_heads;
     const int head_groups = (G + kHeadsPerCta - 1) / kHeadsPerCta;
-    return plan_stream(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits).bytes;
+    return plan_decode(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits).bytes;
 }
 
 extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq,
@@ -881,7 +1678,7 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
 
     const int G = num_q_heads / num_kv_heads;
     const int head_groups = (G + kHeadsPerCta - 1) / kHeadsPerCta;
-    const StreamPlan pl = plan_stream(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits);
+    const StreamPlan pl = plan_decode(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits);
     const size_t need = pl.bytes;
     if (!workspace || workspace_bytes < need)
         return fail(RQ_ERR_WORKSPACE, "rq_decode: workspace of %zu bytes needed, %zu given", need,

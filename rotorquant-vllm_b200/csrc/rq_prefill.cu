@@ -28,6 +28,7 @@
 // Every wait on an mbarrier is bounded; on expiry the CTA records an error, frees its TMEM and
 // returns.
 #include "rq_common.cuh"
+#include "rq_tcgen05.cuh"
 
 namespace rq {
 
@@ -58,71 +59,7 @@ struct PrefillParams {
     int* error_flag;                  // optional device int, set non-zero when a wait expired
 };
 
-// ---- PTX wrappers ------------------------------------------------------------------------
-
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
-}
-// 32 consecutive columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor, no swizzle: operands are stored as 8-row x 16-byte core
-// matrices (128 contiguous bytes each).  lbo / sbo are the byte distances between core matrices
-// along the two tile directions as the tcgen05 descriptor defines them for the operand's major.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) |
-           (static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16) |
-           (static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32) |
-           (1ull << 46);          // descriptor version of sm_100
-}
-
-template <typename T> struct PfType;
-template <> struct PfType<__nv_bfloat16> { static constexpr uint32_t kFmt = 1; };
-template <> struct PfType<__half> { static constexpr uint32_t kFmt = 0; };
+template <typename T> using PfType = TcFormat<T>;
 
 template <typename T>
 __device__ __forceinline__ uint32_t pf_pack(float lo, float hi);
@@ -177,26 +114,6 @@ struct __align__(128) PrefillSmem {
     uint64_t bar_s, bar_o;
     uint32_t tmem_base;
 };
-
-// 64 index bytes of one (token, head) from global memory; `align` is 16, 8 or 4.
-__device__ __forceinline__ void load_idx64(const uint8_t* src, int align, uint32_t (&w)[16]) {
-    if (align == 16) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint4 x = __ldg(reinterpret_cast<const uint4*>(src) + i);
-            w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
-        }
-    } else if (align == 8) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint2 x = __ldg(reinterpret_cast<const uint2*>(src) + i);
-            w[2 * i] = x.x; w[2 * i + 1] = x.y;
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) w[i] = __ldg(reinterpret_cast<const uint32_t*>(src) + i);
-    }
-}
 
 // Four table bytes selected by the four nibbles of sel[15:0]; the table has 8 (BITS 3) or 16
 // (BITS 4) byte entries in 2 or 4 registers.
