@@ -420,6 +420,13 @@ __device__ __forceinline__ void stream_tile(uint32_t (*tbl_k)[8], uint32_t (*tbl
         build_half_int_table<T, NKH>(cbk, norm_k, lo, hi, unscale);
         uint32_t vlo[NVH / 4], vhi[NVH / 4];
         build_half_value_table<T, NVH>(cbv, norm_v, vlo, vhi);
+        if (!valid) {
+            // rows past the end of the sequence may hold bytes that are not index nibbles; with an
+            // all-zero table every PRMT result is zero whatever the selector (a -0.0 entry would
+            // turn a selector with its top bit set into a sign mask, i.e. a NaN pattern in fp16)
+#pragma unroll
+            for (int r = 0; r < NVH / 4; ++r) { vlo[r] = 0u; vhi[r] = 0u; }
+        }
 #pragma unroll
         for (int r = 0; r < NKH / 4; ++r) {
             tbl_k[i][hb * (NKH / 4) + r] = lo[r];
@@ -1062,8 +1069,20 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         const int32_t* bt_row = p.block_table + seq * p.bt_stride;
         const int last_blk = static_cast<int>(p.num_blocks) - 1;
 
-        // slot of this thread's token in a tile (nullptr past the end of the sequence)
-        auto slot_of = [&](int tile) -> const uint8_t* {
+        // Index words and norms of this thread's token, fetched one tile ahead.  Past the end of the
+        // sequence nothing is fetched and the norm is 0, which zeroes the value of every table entry;
+        // the words then keep their last contents, which must still be index words (a nibble with
+        // its top bit set would make PRMT return a sign mask instead of a table byte), hence the
+        // clearing here.
+        uint32_t kw[16], vw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { kw[i] = 0u; vw[i] = 0u; }
+        float nk = 0.0f, nv = 0.0f;
+        bool failed_in = false;
+
+        // ---- where this thread's token of a tile lives ----
+        // cp.async-free direct path: pointer to the token's K index row (nullptr past the end).
+        [[maybe_unused]] auto slot_of = [&](int tile) -> const uint8_t* {
             const int tok = tile * kUTile + tid;
             if (tok >= seq_len) return nullptr;
             const int bi = p.bs_shift >= 0 ? (tok >> p.bs_shift) : (tok / p.block_size);
@@ -1072,78 +1091,74 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
             return p.cache + (static_cast<int64_t>(blk) * p.block_size + off) * p.total_bytes + kvh * kHalfDim;
         };
-        uint32_t kw[16], vw[16];
-        float nk = 0.0f, nv = 0.0f;
-        // TMA path: the warp's elected lane copies the index rows of the warp's 32 tokens of a
-        // tile (two 16-token boxes per region; a 16-token group never straddles a block) into the
-        // warp's staging rows; every call completes one phase of the warp's barrier.
-        [[maybe_unused]] auto issue_tile = [&](int tile) {
-            const int tok0 = tile * kUTile + 32 * warp;
-            int slot[2];
-            bool on[2];
-#pragma unroll
-            for (int g2 = 0; g2 < 2; ++g2) {
-                const int t = tok0 + 16 * g2;
-                on[g2] = t < seq_len;
-                int blk = on[g2] ? __ldg(bt_row + (t >> p.bs_shift)) : 0;
-                blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
-                slot[g2] = (blk << p.bs_shift) + (t & (p.block_size - 1));
+        [[maybe_unused]] auto fetch_direct = [&](int which, const uint8_t* slot, uint32_t (&w)[16], float& norm) {
+            norm = 0.0f;               // a zero norm makes every table entry zero: stale index words are harmless
+            if (slot != nullptr) {
+                if (which) load_idx64(slot + lay.v_idx, v_align, w);
+                else load_idx64(slot + lay.k_idx, 16, w);
+                norm = __ldg(reinterpret_cast<const float*>(slot + (which ? lay.v_norm : lay.k_norm) -
+                                                            kvh * (kHalfDim - 4)));
             }
+        };
+        // TMA path.  A warp stages the index rows of its 32 tokens of the NEXT tile in shared memory
+        // (two 16-token boxes per region; a 16-token group never straddles a block).  Lane l keeps
+        // the block-table entry of its group (l / 16) for the tile after that, loaded a tile early,
+        // and the slot number of its own token in the staged tile (-1 past the end).
+        [[maybe_unused]] int pf_blk = 0, staged_slot = -1;
+        [[maybe_unused]] auto load_blk = [&](int tile) -> int {
+            const int t = tile * kUTile + 32 * warp + (lane & 16);
+            return (tile < t_end && t < seq_len) ? __ldg(bt_row + (t >> p.bs_shift)) : 0;
+        };
+        [[maybe_unused]] auto issue_tile = [&](int tile, int blk) {      // completes one phase of bar_in[warp]
+            const int t = tile * kUTile + 32 * warp + (lane & 16);
+            blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
+            const int gslot = (blk << p.bs_shift) + (t & (p.block_size - 1));
+            const int s0 = __shfl_sync(0xffffffffu, gslot, 0), s1 = __shfl_sync(0xffffffffu, gslot, 16);
+            const bool on0 = tile * kUTile + 32 * warp < seq_len, on1 = tile * kUTile + 32 * warp + 16 < seq_len;
+            staged_slot = (t + (lane & 15) < seq_len) ? gslot + (lane & 15) : -1;
             if (lane == 0) {
                 const uint32_t bar = smem_u32(&sm.bar_in[warp]);
-                const uint32_t bytes = (on[0] ? 2048u : 0u) + (on[1] ? 2048u : 0u);
-                if (bytes != 0) {
-                    mbar_expect_tx(bar, bytes);
-#pragma unroll
-                    for (int g2 = 0; g2 < 2; ++g2) {
-                        if (on[g2]) {
-                            tma_load_2d(smem_u32(sm.stage[warp][0]) + 1024u * g2, &map_idx, kvh * kHalfDim, slot[g2], bar);
-                            tma_load_2d(smem_u32(sm.stage[warp][1]) + 1024u * g2, &map_idx, lay.v_idx + kvh * kHalfDim,
-                                        slot[g2], bar);
-                        }
+                if (on0) {
+                    mbar_expect_tx(bar, on1 ? 4096u : 2048u);
+                    tma_load_2d(smem_u32(sm.stage[warp][0]), &map_idx, kvh * kHalfDim, s0, bar);
+                    tma_load_2d(smem_u32(sm.stage[warp][1]), &map_idx, lay.v_idx + kvh * kHalfDim, s0, bar);
+                    if (on1) {
+                        tma_load_2d(smem_u32(sm.stage[warp][0]) + 1024u, &map_idx, kvh * kHalfDim, s1, bar);
+                        tma_load_2d(smem_u32(sm.stage[warp][1]) + 1024u, &map_idx, lay.v_idx + kvh * kHalfDim, s1, bar);
                     }
                 } else {
                     mbar_arrive(&sm.bar_in[warp]);
                 }
             }
         };
-        [[maybe_unused]] auto read_stage = [&](const uint8_t* rows, uint32_t (&w)[16]) {
+        [[maybe_unused]] auto fetch_staged = [&](int which, uint32_t (&w)[16], float& norm) {
+            norm = 0.0f;
+            if (staged_slot >= 0) {
+                const uint8_t* rows = which ? stage_v : stage_k;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint4 x = *reinterpret_cast<const uint4*>(rows + ((16u * c) ^ stage_sw));
-                w[4 * c] = x.x; w[4 * c + 1] = x.y; w[4 * c + 2] = x.z; w[4 * c + 3] = x.w;
-            }
-        };
-        // index words and norm of this thread's token: K (which == 0) or V (which == 1)
-        auto fetch = [&](int which, const uint8_t* slot, uint32_t (&w)[16], float& norm) {
-            if (slot != nullptr) {
-                if constexpr (TMA) {
-                    read_stage(which ? stage_v : stage_k, w);
-                } else {
-                    if (which) load_idx64(slot + lay.v_idx, v_align, w);
-                    else load_idx64(slot + lay.k_idx, 16, w);
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 x4 = *reinterpret_cast<const uint4*>(rows + ((16u * c) ^ stage_sw));
+                    w[4 * c] = x4.x; w[4 * c + 1] = x4.y; w[4 * c + 2] = x4.z; w[4 * c + 3] = x4.w;
                 }
-                norm = __ldg(reinterpret_cast<const float*>(slot + (which ? lay.v_norm : lay.k_norm) -
-                                                            kvh * (kHalfDim - 4)));
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) w[i] = 0u;
-                norm = 0.0f;
+                norm = __ldg(reinterpret_cast<const float*>(
+                    p.cache + static_cast<int64_t>(staged_slot) * p.total_bytes + (which ? lay.v_norm : lay.k_norm) + 4 * kvh));
             }
         };
-        bool failed_in = false;
         if (!dead) {
-            const uint8_t* first = slot_of(t_begin);
             if constexpr (TMA) {
-                issue_tile(t_begin);
+                issue_tile(t_begin, load_blk(t_begin));
+                pf_blk = load_blk(t_begin + 1);
                 failed_in |= !mbar_wait(&sm.bar_in[warp], ph_in);
                 ph_in ^= 1u;
-            }
-            fetch(0, first, kw, nk);
-            fetch(1, first, vw, nv);
-            if constexpr (TMA) {
+                fetch_staged(0, kw, nk);
+                fetch_staged(1, vw, nv);
                 __syncwarp();
-                if (t_begin + 1 < t_end) issue_tile(t_begin + 1);
+                if (t_begin + 1 < t_end) issue_tile(t_begin + 1, pf_blk);
+                pf_blk = load_blk(t_begin + 2);
+            } else {
+                const uint8_t* first = slot_of(t_begin);
+                fetch_direct(0, first, kw, nk);
+                fetch_direct(1, first, vw, nv);
             }
         }
 
@@ -1194,7 +1209,8 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
 
 #pragma unroll 1
         for (int tile = t_begin; tile < t_end && !dead; ++tile) {
-            const uint8_t* next_slot = tile + 1 < t_end ? slot_of(tile + 1) : nullptr;
+            [[maybe_unused]] const uint8_t* next_slot = nullptr;
+            if constexpr (!TMA) next_slot = tile + 1 < t_end ? slot_of(tile + 1) : nullptr;
             const bool valid = tile * kUTile + tid < seq_len;
             bool failed = failed_in;
             failed_in = false;
@@ -1221,9 +1237,11 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 if (tile + 1 < t_end) {                  // the staged rows of the next tile
                     failed |= !mbar_wait(&sm.bar_in[warp], ph_in);
                     ph_in ^= 1u;
+                    fetch_staged(0, kw, nk);
                 }
+            } else {
+                fetch_direct(0, next_slot, kw, nk);
             }
-            fetch(0, next_slot, kw, nk);
             tc_fence_before();
             __syncthreads();
             if (tid == 0) {
@@ -1257,10 +1275,13 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                                    prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
                 }
             }
-            fetch(1, next_slot, vw, nv);
             if constexpr (TMA) {
+                if (tile + 1 < t_end) fetch_staged(1, vw, nv);
                 __syncwarp();                            // the staging rows are free again
-                if (tile + 2 < t_end) issue_tile(tile + 2);
+                if (tile + 2 < t_end) issue_tile(tile + 2, pf_blk);
+                pf_blk = load_blk(tile + 3);
+            } else {
+                fetch_direct(1, next_slot, vw, nv);
             }
 
             // ---- 4: scores, lazy reference maximum, probabilities ----

@@ -141,3 +141,39 @@ def test_argument_checks_mirror_the_reference():
     with pytest.raises(ValueError, match="diagonal"):
         _decode(g["q"], g["kv_cache"], g["block_table"], g["seq_lens"], g["k_centroids"],
                 g["v_centroids"], bad_R, 8, 128, 16)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_bytes_past_the_end_of_a_sequence_are_ignored(dtype):
+    """Slots of the last block beyond seq_len may hold anything (a recycled or never written
+    block): fill them with 0xFF bytes, which are neither index nibbles nor finite norms."""
+    c = _fresh_case("iso_fast", 3, 3, 4, 16, [130, 17, 200, 1], 16, dtype, seed=11)
+    cache = c["kv_cache"].clone()
+    bs = cache.shape[1]
+    for s, n in enumerate(c["seq_lens"].tolist()):
+        nblk = (n + bs - 1) // bs
+        last = int(c["block_table"][s, nblk - 1])
+        used = n - (nblk - 1) * bs
+        cache[last, used:] = 0xFF
+    c2 = dict(c)
+    c2["kv_cache"] = cache
+    out = _run_case(c2)
+    _assert_close(out, _oracle(c), _oracle(c, rotated=True), dtype, "garbage tail")
+
+
+def test_streaming_kernels_in_a_subprocess():
+    """RQ_DECODE_PATH=stream selects the warp-streaming kernel (read once per process), with and
+    without its TMA ring: run the golden and edge cases under it in child processes."""
+    import os
+    import subprocess
+    import sys
+
+    if os.environ.get("RQ_DECODE_PATH") == "stream":
+        pytest.skip("already running under the streaming kernel")
+    here = os.path.dirname(os.path.abspath(__file__))
+    for extra in ({"RQ_DECODE_PATH": "stream"}, {"RQ_DECODE_PATH": "stream", "RQ_DECODE_NO_TMA": "1"}):
+        env = dict(os.environ, **extra)
+        res = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_decode_gpu.py"), "-x", "-q",
+                              "-m", "gpu", "-k", "golden or past_the_end or fresh or rotated_space"],
+                             env=env, capture_output=True, text=True, timeout=900)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
