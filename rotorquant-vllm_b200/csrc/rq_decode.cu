@@ -989,7 +989,8 @@ __device__ __forceinline__ Table<BITS> build_value_table(const float* cb, float 
     return t;
 }
 
-template <typename T, int KB, int VB, bool TMA>
+// NH = query heads computed per item: 4 when the GQA group has at most 4 heads, else 8.
+template <typename T, int KB, int VB, bool TMA, int NH>
 __global__ void __launch_bounds__(kUThreads, kUCtasPerSm)
 decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_idx) {
     extern __shared__ uint8_t smem_raw[];
@@ -1164,7 +1165,7 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
 
         // ---- queries of this item: rotate, round, quantise to signed digit planes (B operand) ----
 #pragma unroll 1
-        for (int round = 0; round < 2; ++round) {
+        for (int round = 0; round < NH / 4; ++round) {
             const int h = 4 * round + warp;
             float r[4] = {0.f, 0.f, 0.f, 0.f};
             if (h < heads_here) {
@@ -1202,9 +1203,9 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         fence_async_proxy();
         __syncthreads();
 
-        float m_ref[kHeadsPerCta], l_acc[kHeadsPerCta];
+        float m_ref[NH], l_acc[NH];
 #pragma unroll
-        for (int h = 0; h < kHeadsPerCta; ++h) { m_ref[h] = -INFINITY; l_acc[h] = 0.0f; }
+        for (int h = 0; h < NH; ++h) { m_ref[h] = -INFINITY; l_acc[h] = 0.0f; }
         bool pv_pending = false;
 
 #pragma unroll 1
@@ -1288,7 +1289,7 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             failed |= !mbar_wait(&sm.bar_s, ph_s);
             ph_s ^= 1u;
             tc_fence_after();
-            float sc[kHeadsPerCta];
+            float sc[NH];
             const float tok_bias = valid ? 0.0f : -INFINITY;
             {
                 uint32_t d[32];
@@ -1297,7 +1298,7 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 const float4 qf1 = *reinterpret_cast<const float4*>(&sm.qf[4]);
                 const float qf[8] = {qf0.x, qf0.y, qf0.z, qf0.w, qf1.x, qf1.y, qf1.z, qf1.w};
 #pragma unroll
-                for (int h = 0; h < kHeadsPerCta; ++h) {
+                for (int h = 0; h < NH; ++h) {
                     // d[h] = Khi.Qhi, d[8+h] = Khi.Qlo, d[16+h] = Klo.Qhi, d[24+h] = Klo.Qlo
                     const int t1 = static_cast<int>(d[h]) * 256 + (static_cast<int>(d[8 + h]) + static_cast<int>(d[16 + h]));
                     const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(static_cast<int>(d[24 + h])));
@@ -1308,12 +1309,12 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             }
             bool grow = false;
 #pragma unroll
-            for (int h = 0; h < kHeadsPerCta; ++h) grow |= sc[h] > m_ref[h] + 8.0f;
+            for (int h = 0; h < NH; ++h) grow |= sc[h] > m_ref[h] + 8.0f;
             if (__syncthreads_or(grow || failed)) {
                 if (__syncthreads_or(failed)) { dead = true; break; }
                 // move the reference maxima: CTA-wide maximum per head, rescale sums and O^T
 #pragma unroll
-                for (int h = 0; h < kHeadsPerCta; ++h) {
+                for (int h = 0; h < NH; ++h) {
                     float m = sc[h];
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -1322,7 +1323,9 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 __syncthreads();
                 float alpha[kHeadsPerCta];
 #pragma unroll
-                for (int h = 0; h < kHeadsPerCta; ++h) {
+                for (int h = NH; h < kHeadsPerCta; ++h) alpha[h] = 1.0f;
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
                     const float m_tile = fmaxf(fmaxf(sm.red[0][h], sm.red[1][h]), fmaxf(sm.red[2][h], sm.red[3][h]));
                     const float m_new = fmaxf(m_ref[h], m_tile);
                     alpha[h] = (m_new == -INFINITY) ? 1.0f : ex2_approx(m_ref[h] - m_new);   // 0 on the first tile
@@ -1340,15 +1343,15 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 }
             }
             {
-                float pr[kHeadsPerCta];
+                float pr[NH];
 #pragma unroll
-                for (int h = 0; h < kHeadsPerCta; ++h) {
+                for (int h = 0; h < NH; ++h) {
                     pr[h] = ex2_approx(sc[h] - m_ref[h]);
                     l_acc[h] += pr[h];
                 }
-                uint32_t ph[4], pl[4];
+                uint32_t ph[4] = {0u, 0u, 0u, 0u}, pl[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < NH / 2; ++j) {
                     ph[j] = pack_pair<T>(pr[2 * j], pr[2 * j + 1]);
                     const float2 back = unpack_pair<T>(ph[j]);
                     pl[j] = pack_pair<T>(pr[2 * j] - back.x, pr[2 * j + 1] - back.y);
@@ -1380,7 +1383,7 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             if (__syncthreads_or(failed)) dead = true;
         }
 #pragma unroll
-        for (int h = 0; h < kHeadsPerCta; ++h) {
+        for (int h = 0; h < NH; ++h) {
             float v = l_acc[h];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -1391,7 +1394,7 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         if (tid < heads_here) {
             float m = m_ref[0];
 #pragma unroll
-            for (int h = 1; h < kHeadsPerCta; ++h) m = tid == h ? m_ref[h] : m;
+            for (int h = 1; h < NH; ++h) m = tid == h ? m_ref[h] : m;
             const float l = (sm.red[0][tid] + sm.red[1][tid]) + (sm.red[2][tid] + sm.red[3][tid]);
             p.ws_m[row * kHeadsPerCta + tid] = m;
             p.ws_l[row * kHeadsPerCta + tid] = dead ? __int_as_float(0x7fc00000) : l;
@@ -1401,7 +1404,7 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             tmem_ld16_nowait(lane_base + kUColO, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int h = 0; h < kHeadsPerCta; ++h)     // lane (position) x holds head-dim x ^ 1
+            for (int h = 0; h < NH; ++h)               // lane (position) x holds head-dim x ^ 1
                 if (h < heads_here)
                     p.ws_o[(row * kHeadsPerCta + h) * kHeadDim + (tid ^ 1)] =
                         __uint_as_float(o[h]) + __uint_as_float(o[8 + h]);
@@ -1625,13 +1628,15 @@ static int launch_decode(const DecodeParams& p, int num_seqs, cudaStream_t st) {
     if (umma) {
         const size_t smem = sizeof(UmmaSmem) + 512;                              // + hand alignment
         const long long ctas = 1LL * p.stream_groups * p.H * p.head_groups;
-        if (tma) {
-            if (int e = ensure_smem(decode_umma_kernel<T, KB, VB, true>, smem)) return e;
-            decode_umma_kernel<T, KB, VB, true><<<static_cast<unsigned>(ctas), kUThreads, smem, st>>>(p, map_idx);
-        } else {
-            if (int e = ensure_smem(decode_umma_kernel<T, KB, VB, false>, smem)) return e;
-            decode_umma_kernel<T, KB, VB, false><<<static_cast<unsigned>(ctas), kUThreads, smem, st>>>(p, map_idx);
-        }
+        auto launch = [&](auto kernel) -> int {
+            if (int e = ensure_smem(kernel, smem)) return e;
+            kernel<<<static_cast<unsigned>(ctas), kUThreads, smem, st>>>(p, map_idx);
+            return RQ_OK;
+        };
+        const bool few = p.G <= 4;                                               // at most 4 query heads per item
+        if (int e = tma ? (few ? launch(decode_umma_kernel<T, KB, VB, true, 4>) : launch(decode_umma_kernel<T, KB, VB, true, 8>))
+                        : (few ? launch(decode_umma_kernel<T, KB, VB, false, 4>) : launch(decode_umma_kernel<T, KB, VB, false, 8>)))
+            return e;
         if (int e = check_cuda(cudaGetLastError(), "rq_decode tensor-memory launch")) return e;
     } else {
         if (tma) tma = encode_cache_map(&map_norm, p.cache, num_slots, p.total_bytes, kNormBox, CU_TENSOR_MAP_SWIZZLE_NONE);
