@@ -44,7 +44,7 @@ UNIT = "tokens/s"
 # DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of
 # decode_split_kernel) divided by the algorithmic bytes of the same launch; see
 # profiles/decode_split_kernel_llama8b.md.  Used to scale `roofline.traffic` to this run's launch.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 156.3e6 / 143.2e6
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 156.5e6 / 143.2e6
 
 
 def parse_args():
@@ -465,7 +465,7 @@ def run_gpu_arm(args, w: syn.Workload) -> None:
             "e2e": {"value": seqs_per_step / (e2e_ms / args.steps * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": 4 * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "decode_stream_kernel (+ plan and merge kernels)",
+            "roofline": {"bound": "hbm", "kernel": "decode_umma_kernel (+ plan and merge kernels)",
                          "achieved": achieved, "peak": peak, "peak_kind": f"{peak_kind} copy bandwidth",
                          "unit": "GB/s", "frac": achieved / peak,
                          "algorithmic_bytes": alg, "kernel_ms": decode_ms,

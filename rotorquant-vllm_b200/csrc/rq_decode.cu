@@ -4,11 +4,14 @@
 // Triton kernel (one program per (sequence, query head), CUDA-core dot products, no split-KV)
 // and the two dense 128x128 rotations its launcher runs around it.
 //
-// Work decomposition.  Three launches: a one-CTA prefix sum of the tiles per sequence, the
-// streaming kernel (see below: every warp of a fixed grid streams an equal share of the
-// (sequence, 16-token tile) space for one KV head, with a private cp.async ring, so the 136
-// payload bytes of a (token, KV head) are read from HBM exactly once for all query heads of the
-// GQA group), and a merge kernel that combines the partial results, rounds, and applies R.
+// Work decomposition.  Three launches: a one-CTA prefix sum of the tiles per sequence, an attention
+// kernel that streams equal shares of the (sequence, tile) space per KV head and leaves partial
+// results, and a merge kernel that combines them, rounds, and applies R.  The 136 payload bytes of
+// a (token, KV head) are read from HBM exactly once for all query heads of the GQA group.  Two
+// attention kernels share that frame:
+//   decode_umma_kernel    (default) one thread per token, tcgen05 MMAs with TMEM accumulators, the
+//                         K tile as a TMEM A operand, TMA-staged index rows;
+//   decode_stream_kernel  (RQ_DECODE_PATH=stream) one warp per 16-token tile, mma.sync.
 //
 // Arithmetic (matches "reference decompress + SDPA"):
 //   q_rot   = round_T(q @ R^T)            exact FMA chain per 4x4 block, computed in the prologue
@@ -19,9 +22,10 @@
 //   P @ V   = tensor-core mma with P split into hi + lo parts (two T-precision terms, ~16 bits),
 //             fp32 accumulate
 //   out     = round_T(round_T(o / l) @ R)  in the merge kernel
-// mma.sync m16n8k16 is used on purpose: M is the 4..8 query heads of one KV head, far below the
-// 128-row tiles tcgen05 needs, and the kernel is bound by HBM bytes and dequantisation
-// instructions, not by tensor throughput.
+// Both kernels are bound by the dequantisation instructions (one byte permute per V value, half
+// of one per K value), not by tensor throughput; the tcgen05 kernel wins by putting the 128 tokens
+// of a tile on the M side (M = tokens for S^T, M = head-dims for O^T), which removes the per-warp
+// MMA, ldmatrix and fragment bookkeeping of the mma.sync formulation.
 #include <cuda.h>          // CUtensorMap (types only; the encoder is looked up at run time)
 
 #include <cstdlib>
