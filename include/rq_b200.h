@@ -110,6 +110,9 @@ size_t rq_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads
  *   max_seq_len   upper bound of seq_lens (host value; sizes the grid, never read from device)
  *   workspace     >= rq_decode_workspace_bytes(...) bytes, 16-byte aligned
  *   num_splits    context splits per sequence, 0 = automatic
+ *
+ * Every device-side wait of the kernels (mbarriers of TMA copies and tcgen05 MMAs) is bounded to
+ * about one second of SM clocks; if one expires the affected outputs are NaN and the kernels return.
  */
 int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq, int64_t q_stride_head,
               int64_t o_stride_seq, int64_t o_stride_head, int num_seqs, int num_q_heads,
