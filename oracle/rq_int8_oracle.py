@@ -15,9 +15,10 @@ Scheme, per (sequence, KV head), queries and keys in rotated space:
   q_i8[m]     = rint(q_rot[m] * (127 / max|q_rot[m]|)),       q_scale[m] = max|q_rot[m]| / 127
   table[t][i] = round_T(centroid_k[i] * norm_k[t]);  code[t][i] = rint(table * (127 / max_i|table|))
   k_i8[t][d]  = code[t][idx[t][d]],                           k_scale[t] = max_i|table[t][i]| / 127
-  s[m][t]     = float(q_i8[m] . k_i8[t]) * ((q_scale[m] * sm_scale*log2 e) * k_scale[t])
-  online softmax over 128-key tiles in base 2; P is rounded to T before it multiplies V and before
-  it enters the row sum; V = round_T(centroid_v[idx] * norm_v) exactly as decompressed;
+  s[m][t]     = (float(q_i8[m] . k_i8[t]) * k_scale[t]) * (q_scale[m] * sm_scale*log2 e)
+  online softmax over 128-key tiles in base 2 against a lazy reference maximum (it moves to the tile
+  maximum only when that exceeds it by more than 8); P is rounded to T before it multiplies V, the row
+  sum adds the unrounded values; V = round_T(centroid_v[idx] * norm_v) exactly as decompressed;
   out         = round_T(round_T(O / l) @ R)
 """
 
@@ -89,17 +90,20 @@ def prefill_int8(q, kv_cache, block_table, seq_lens, centroids_k, centroids_v, r
             for j in range((n + TILE - 1) // TILE):
                 k0, k1 = j * TILE, min(n, (j + 1) * TILE)
                 dots = torch.einsum("tgd,kd->tgk", q_i8, k_i8[k0:k1, h])                    # exact integers
-                sc = dots * (row_factor.unsqueeze(-1) * k_scale[k0:k1, h].view(1, 1, -1))
+                sk = dots * k_scale[k0:k1, h].view(1, 1, -1)                               # scaled by the key
                 allowed = (torch.arange(k0, k1).view(1, 1, -1) <= pos.view(-1, 1, 1))
-                sc = torch.where(allowed, sc, torch.full_like(sc, float("-inf")))
-                m_new = torch.maximum(m_run, sc.amax(-1))
+                sk_max = torch.where(allowed, sk, torch.full_like(sk, float("-inf"))).amax(-1)
+                sc = torch.where(allowed, sk * row_factor.unsqueeze(-1), torch.full_like(sk, float("-inf")))
+                # lazy reference: it moves only when the tile maximum exceeds it by more than 2^8
+                m_tile = sk_max * row_factor
+                grew = m_tile > m_run + 8.0
+                m_new = torch.where(grew, m_tile, m_run)
                 m_use = torch.where(torch.isinf(m_new), torch.zeros_like(m_new), m_new)
-                alpha = torch.where(m_new == m_run, torch.ones_like(m_new),
-                                    torch.where(torch.isinf(m_run), torch.zeros_like(m_new),
-                                                torch.exp2(m_run - m_use)))
+                alpha = torch.where(grew, torch.where(torch.isinf(m_run), torch.zeros_like(m_new),
+                                                      torch.exp2(m_run - m_use)), torch.ones_like(m_new))
                 p = torch.where(allowed, torch.exp2(sc - m_use.unsqueeze(-1)), torch.zeros_like(sc))
+                l_run = l_run * alpha + p.sum(-1)                                          # unrounded sum
                 p = p.to(dtype).to(torch.float32)
-                l_run = l_run * alpha + p.sum(-1)
                 acc = acc * alpha.unsqueeze(-1) + torch.einsum("tgk,kd->tgd", p, v_all[k0:k1, h])
                 m_run = m_new
             inv_l = torch.where(l_run > 0, 1.0 / l_run, torch.zeros_like(l_run))

@@ -27,12 +27,14 @@
 //
 // Every wait on an mbarrier is bounded; on expiry the CTA records an error, frees its TMEM and
 // returns.
+#include <type_traits>
+
 #include "rq_common.cuh"
 #include "rq_tcgen05.cuh"
 
 namespace rq {
 
-constexpr int kPfThreads = 128;
+constexpr int kPfThreads = 256;       // two threads per row / key
 constexpr int kPfRows = 128;          // MMA M
 constexpr int kPfKeys = 128;          // keys per tile (MMA N of S, K extent of P V)
 constexpr uint32_t kTmemCols = 256;   // S: columns 0..127 (int32), O: columns 128..255 (fp32)
@@ -109,11 +111,32 @@ struct __align__(128) PrefillSmem {
     uint16_t v[kPfKeys * kHeadDim];
     uint16_t p[kPfRows * kPfKeys];
     float k_scale[kPfKeys];
+    float xch[2][kPfRows];            // exchange between the two threads of a row
     float rot[32 * 16];
     float cb[2][16];
     uint64_t bar_s, bar_o;
     uint32_t tmem_base;
 };
+
+// 32 index bytes (half a row) of one (token, head) from global memory; `align` is 16, 8 or 4.
+__device__ __forceinline__ void load_idx32(const uint8_t* src, int align, uint32_t (&w)[8]) {
+    if (align == 16) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(src) + i);
+            w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
+        }
+    } else if (align == 8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint2 x = __ldg(reinterpret_cast<const uint2*>(src) + i);
+            w[2 * i] = x.x; w[2 * i + 1] = x.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = __ldg(reinterpret_cast<const uint32_t*>(src) + i);
+    }
+}
 
 // Four table bytes selected by the four nibbles of sel[15:0]; the table has 8 (BITS 3) or 16
 // (BITS 4) byte entries in 2 or 4 registers.
@@ -130,14 +153,24 @@ __device__ __forceinline__ uint32_t byte_lookup(const uint32_t* tbl, uint32_t se
     }
 }
 
+// Barrier of the two warps that share 32 rows (warp w and w ^ 4): ids 1..4.
+__device__ __forceinline__ void pair_sync(int quarter) {
+    asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory");
+}
+
+// 256 threads: thread (row = tid % 128, half = tid / 128).  Row r is TMEM lane r; the two threads
+// of a row sit in warps w and w + 4, which may both address the lane quarter w % 4.  In the
+// dequantisation phase `row` is the key of the tile and `half` the half of its 128 head-dims; in
+// the softmax phase `row` is the query row and `half` the half of the 128 keys of the tile.
 template <typename T, int KB, int VB>
-__global__ void __launch_bounds__(kPfThreads)
+__global__ void __launch_bounds__(kPfThreads, 2)
 prefill_int8_kernel(const PrefillParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     PrefillSmem& sm = *reinterpret_cast<PrefillSmem*>(smem_raw);
     constexpr int NK = 1 << KB, NV = 1 << VB;
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    const int row = tid & (kPfRows - 1), half = tid >> 7, quarter = warp & 3;
     const int kvh = blockIdx.y, seq = blockIdx.z;
     const int q_begin = p.cu_seqlens_q ? __ldg(p.cu_seqlens_q + seq) : 0;
     const int q_end = p.cu_seqlens_q ? __ldg(p.cu_seqlens_q + seq + 1) : p.num_tokens;
@@ -148,8 +181,8 @@ prefill_int8_kernel(const PrefillParams p) {
     const int m_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
     if (m_tile >= tiles_m || kv_len == 0) {
         // rows of an empty sequence still get a defined (zero) output
-        if (m_tile < tiles_m) {
-            const int tl = tid / p.G, h = tid % p.G;
+        if (m_tile < tiles_m && half == 0) {
+            const int tl = row / p.G, h = row % p.G;
             const int tok = m_tile * p.tokens_per_tile + tl;
             if (tl < p.tokens_per_tile && tok < q_len) {
                 T* dst = static_cast<T*>(p.out) + (q_begin + tok) * p.o_stride_tok +
@@ -160,8 +193,8 @@ prefill_int8_kernel(const PrefillParams p) {
         return;
     }
 
-    // this thread's row: query token and head; absolute position of the token in its sequence
-    const int tok_local = tid / p.G, head_local = tid % p.G;
+    // this thread's query row: token and head; absolute position of the token in its sequence
+    const int tok_local = row / p.G, head_local = row % p.G;
     const int tok = m_tile * p.tokens_per_tile + tok_local;
     const bool row_valid = tok_local < p.tokens_per_tile && tok < q_len;
     const int pos = row_valid ? kv_len - q_len + tok : -1;
@@ -189,10 +222,11 @@ prefill_int8_kernel(const PrefillParams p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
-    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(tid) << 16);   // TMEM lane = row
-    const uint32_t core_row_off = (tid >> 3) * 1024 + (tid & 7) * 16;       // q/k tiles: 8 chunks per row group
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);   // this warp's TMEM lanes
+    const uint32_t core_row_off = (row >> 3) * 1024 + (row & 7) * 16;                // q/k tiles: 8 chunks per row group
 
-    // ---- Q: rotate, round, quantise this row to int8 ----
+    // ---- Q: rotate, round, quantise the row to int8; each of the row's two threads rotates the
+    //      whole row (the scale needs its maximum) and stores its half ----
     float q_scale = 0.0f;
     {
         uint32_t packed[64];                    // rotated, rounded row as T pairs (d, d+1)
@@ -228,6 +262,7 @@ prefill_int8_kernel(const PrefillParams p) {
         q_scale = ok ? __fdiv_rn(mx, 127.0f) : 0.0f;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {           // 16 head-dims = 16 bytes per chunk
+            if ((c >> 2) != half) continue;
             uint32_t wds[4];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -252,31 +287,36 @@ prefill_int8_kernel(const PrefillParams p) {
     const int v_align = (lay.v_idx % 16 == 0) ? 16 : ((lay.v_idx % 8 == 0) ? 8 : 4);
     const int32_t* bt_row = p.block_table + seq * p.bt_stride;
 
-    float m_run = -INFINITY, l_run = 0.0f;
-    uint32_t phase = 0;
-    bool failed = false;
+    // index words and norms of this thread's half key, fetched one tile ahead
+    uint32_t kw[8], vw[8];
+    float norm_k = 0.0f, norm_v = 0.0f;
+    auto load_key = [&](int tile) {
+        const int kt = tile * kPfKeys + row;
+        norm_k = 0.0f;
+        norm_v = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { kw[i] = 0u; vw[i] = 0u; }
+        if (tile < n_tiles && kt < kv_len) {
+            int64_t blk = __ldg(bt_row + kt / p.block_size);
+            blk = blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
+            const uint8_t* slot = p.cache + (blk * p.block_size + kt % p.block_size) * p.total_bytes;
+            load_idx32(slot + lay.k_idx + kvh * kHalfDim + 32 * half, 16, kw);
+            load_idx32(slot + lay.v_idx + kvh * kHalfDim + 32 * half, v_align, vw);
+            norm_k = __ldg(reinterpret_cast<const float*>(slot + lay.k_norm) + kvh);
+            norm_v = __ldg(reinterpret_cast<const float*>(slot + lay.v_norm) + kvh);
+        }
+    };
+    load_key(0);
+
+    float m_run = -INFINITY, l_run = 0.0f;      // l_run: sum over this thread's half of the keys
+    uint32_t ph_s = 0, ph_o = 0;
+    bool pv_pending = false, failed = false;
 
 #pragma unroll 1
     for (int j = 0; j < n_tiles; ++j) {
-        // ---- 1. dequantise key j*128 + tid: K codes + scale, V values ----
+        // ---- 1. dequantise half of key j*128 + row: K codes + scale, then V values ----
         {
-            const int kt = j * kPfKeys + tid;
-            const bool valid = kt < kv_len;
-            uint32_t kw[16], vw[16];
-            float norm_k = 0.0f, norm_v = 0.0f;
-            if (valid) {
-                int64_t blk = __ldg(bt_row + kt / p.block_size);
-                blk = blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
-                const uint8_t* slot = p.cache + (blk * p.block_size + kt % p.block_size) * p.total_bytes;
-                load_idx64(slot + lay.k_idx + kvh * kHalfDim, 16, kw);
-                load_idx64(slot + lay.v_idx + kvh * kHalfDim, v_align, vw);
-                norm_k = __ldg(reinterpret_cast<const float*>(slot + lay.k_norm) + kvh);
-                norm_v = __ldg(reinterpret_cast<const float*>(slot + lay.v_norm) + kvh);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) { kw[i] = 0u; vw[i] = 0u; }
-            }
-            // K: int8 code table of this key
+            // K: int8 code table of this key (both threads of the key build it)
             float tv[NK];
             float mx = 0.0f;
 #pragma unroll
@@ -286,7 +326,7 @@ prefill_int8_kernel(const PrefillParams p) {
             }
             const bool ok = mx > 0.0f && mx <= 3.0e38f;
             const float inv = ok ? __fdiv_rn(127.0f, mx) : 0.0f;
-            sm.k_scale[tid] = ok ? __fdiv_rn(mx, 127.0f) : 0.0f;
+            if (half == 0) sm.k_scale[row] = ok ? __fdiv_rn(mx, 127.0f) : 0.0f;
             uint32_t ktbl[NK / 4];
 #pragma unroll
             for (int i = 0; i < NK / 4; ++i) {
@@ -295,13 +335,20 @@ prefill_int8_kernel(const PrefillParams p) {
                 ktbl[i] = (c0 & 0xFF) | ((c1 & 0xFF) << 8) | ((c2 & 0xFF) << 16) | ((c3 & 0xFF) << 24);
             }
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < 4; ++c) {           // chunks 4*half .. 4*half + 3 of the key's 8
                 const uint32_t a = kw[2 * c], b = kw[2 * c + 1];
-                *reinterpret_cast<uint4*>(&sm.k[core_row_off + c * 128]) =
+                *reinterpret_cast<uint4*>(&sm.k[core_row_off + (4 * half + c) * 128]) =
                     make_uint4(byte_lookup<KB>(ktbl, a), byte_lookup<KB>(ktbl, a >> 16),
                                byte_lookup<KB>(ktbl, b), byte_lookup<KB>(ktbl, b >> 16));
             }
-            // V: exact decompressed values, low- and high-byte planes of the T bit patterns
+            // V: the previous tile's P V reads v and p until its barrier completes
+            if (pv_pending) {
+                failed |= !mbar_wait(&sm.bar_o, ph_o);
+                ph_o ^= 1u;
+                tc_fence_after();
+                pv_pending = false;
+            }
+            // exact decompressed values, low- and high-byte planes of the T bit patterns
             uint32_t vlo[NV / 4], vhi[NV / 4];
 #pragma unroll
             for (int i = 0; i < NV / 4; ++i) {
@@ -310,16 +357,17 @@ prefill_int8_kernel(const PrefillParams p) {
                 vlo[i] = prmt(p01, p23, 0x6420);
                 vhi[i] = prmt(p01, p23, 0x7531);
             }
-            uint8_t* vdst = reinterpret_cast<uint8_t*>(sm.v) + (tid >> 3) * (16 * 128) + (tid & 7) * 16;
+            uint8_t* vdst = reinterpret_cast<uint8_t*>(sm.v) + (row >> 3) * (16 * 128) + (row & 7) * 16;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {       // 8 head-dims = one 32-bit index word per chunk
+            for (int c = 0; c < 8; ++c) {        // 8 head-dims = one 32-bit index word per chunk
                 const uint32_t lo0 = byte_lookup<VB>(vlo, vw[c]), hi0 = byte_lookup<VB>(vhi, vw[c]);
                 const uint32_t lo1 = byte_lookup<VB>(vlo, vw[c] >> 16), hi1 = byte_lookup<VB>(vhi, vw[c] >> 16);
-                *reinterpret_cast<uint4*>(vdst + c * 128) =
+                *reinterpret_cast<uint4*>(vdst + (8 * half + c) * 128) =
                     make_uint4(prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
                                prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
             }
         }
+        load_key(j + 1);                             // lands while this tile's softmax runs
         fence_async_proxy();
         tc_fence_before();
         __syncthreads();
@@ -333,63 +381,87 @@ prefill_int8_kernel(const PrefillParams p) {
                           idesc_s, s > 0 ? 1u : 0u);
             tc_commit(&sm.bar_s);
         }
-        if (__syncthreads_or(!mbar_wait(&sm.bar_s, phase))) { failed = true; break; }   // uniform exit
+        failed |= !mbar_wait(&sm.bar_s, ph_s);
+        ph_s ^= 1u;
         tc_fence_after();
 
-        // ---- 3. online softmax on this thread's row; P -> shared memory ----
-        const int key0 = j * kPfKeys;
-        float m_tile = -INFINITY;
+        // ---- 3. online softmax: this thread's row, keys 64*half .. 64*half + 63 of the tile ----
+        // keys of this half that the row may see: columns 0 .. limit (>= 63: all of them)
+        const int limit = pos - (j * kPfKeys + 64 * half);
+        const bool unmasked = __all_sync(0xffffffffu, limit >= 63);
+        uint8_t* prow = reinterpret_cast<uint8_t*>(sm.p) + (row >> 3) * (16 * 128) + (row & 7) * 16;
+        auto softmax_half = [&](auto masked_tag) {
+            constexpr bool kMasked = decltype(masked_tag)::value;
+            // pass A: scale the integer sums by the key scales (kept in TMEM as floats), row maximum
+            float m_half = -INFINITY;
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(lane_addr + 32 * ch, r);
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const float s = static_cast<float>(static_cast<int>(r[c])) * (row_factor * sm.k_scale[32 * ch + c]);
-                if (key0 + 32 * ch + c <= pos) m_tile = fmaxf(m_tile, s);
-            }
-        }
-        const float m_new = fmaxf(m_run, m_tile);
-        const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-        const float alpha = (m_new == m_run) ? 1.0f : ((m_run == -INFINITY) ? 0.0f : pf_ex2(m_run - m_use));
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
+            for (int ch = 0; ch < 2; ++ch) {
                 uint32_t r[32];
-                tmem_ld32(lane_addr + kPfKeys + 32 * ch, r);
+                tmem_ld32(lane_base + 64 * half + 32 * ch, r);
 #pragma unroll
-                for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-                tmem_st32(lane_addr + kPfKeys + 32 * ch, r);
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const float4 ks = *reinterpret_cast<const float4*>(&sm.k_scale[64 * half + 32 * ch + 4 * c4]);
+                    const float kk[4] = {ks.x, ks.y, ks.z, ks.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = 4 * c4 + e;
+                        const float sv = static_cast<float>(static_cast<int>(r[c])) * kk[e];
+                        r[c] = __float_as_uint(sv);
+                        if (!kMasked || 32 * ch + c <= limit) m_half = fmaxf(m_half, sv);
+                    }
+                }
+                tmem_st32(lane_base + 64 * half + 32 * ch, r);
             }
-        }
-        l_run *= alpha;
-        m_run = m_new;
-        uint8_t* prow = reinterpret_cast<uint8_t*>(sm.p) + (tid >> 3) * (16 * 128) + (tid & 7) * 16;
+            sm.xch[half][row] = m_half;
+            pair_sync(quarter);
+            const float m_tile = fmaxf(m_half, sm.xch[half ^ 1][row]) * row_factor;     // row_factor >= 0
+            // lazy reference: it moves only when the tile maximum exceeds it by more than 2^8
+            const bool grew = m_tile > m_run + 8.0f;
+            const float m_new = grew ? m_tile : m_run;
+            const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+            const float alpha = grew ? ((m_run == -INFINITY) ? 0.0f : pf_ex2(m_run - m_use)) : 1.0f;
+            if (j > 0 && __any_sync(0xffffffffu, grew)) {                // this thread's half of the O columns
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(lane_addr + 32 * ch, r);
-            uint32_t pk[16];
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_base + kPfKeys + 64 * half + 32 * ch, r);
 #pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-                const float s0 = static_cast<float>(static_cast<int>(r[c])) * (row_factor * sm.k_scale[32 * ch + c]);
-                const float s1 = static_cast<float>(static_cast<int>(r[c + 1])) * (row_factor * sm.k_scale[32 * ch + c + 1]);
-                const float p0 = (key0 + 32 * ch + c <= pos) ? pf_ex2(s0 - m_use) : 0.0f;
-                const float p1 = (key0 + 32 * ch + c + 1 <= pos) ? pf_ex2(s1 - m_use) : 0.0f;
-                pk[c >> 1] = pf_pack<T>(p0, p1);
-                const float2 back = pf_unpack<T>(pk[c >> 1]);     // the row sum uses what the MMA sees
-                l_run += back.x + back.y;
+                    for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+                    tmem_st32(lane_base + kPfKeys + 64 * half + 32 * ch, r);
+                }
             }
+            l_run *= alpha;
+            m_run = m_new;
+            // pass B: probabilities -> shared P tile (K-major: 16 chunks of 8 keys per row)
+#pragma unroll 1
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t r[32];
+                tmem_ld32(lane_base + 64 * half + 32 * ch, r);
+                uint32_t pk[16];
 #pragma unroll
-            for (int kc = 0; kc < 4; ++kc)
-                *reinterpret_cast<uint4*>(prow + (4 * ch + kc) * 128) =
-                    make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
-        }
+                for (int c = 0; c < 32; c += 2) {
+                    float p0 = pf_ex2(fmaf(__uint_as_float(r[c]), row_factor, -m_use));
+                    float p1 = pf_ex2(fmaf(__uint_as_float(r[c + 1]), row_factor, -m_use));
+                    if (kMasked) {
+                        if (32 * ch + c > limit) p0 = 0.0f;
+                        if (32 * ch + c + 1 > limit) p1 = 0.0f;
+                    }
+                    l_run += p0 + p1;
+                    pk[c >> 1] = pf_pack<T>(p0, p1);
+                }
+#pragma unroll
+                for (int kc = 0; kc < 4; ++kc)
+                    *reinterpret_cast<uint4*>(prow + (8 * half + 4 * ch + kc) * 128) =
+                        make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
+            }
+        };
+        if (unmasked) softmax_half(std::false_type{});
+        else softmax_half(std::true_type{});
         fence_async_proxy();
         tc_fence_before();
-        __syncthreads();
+        if (__syncthreads_or(failed)) { failed = true; break; }      // uniform exit
 
-        // ---- 4. O += P V ----
+        // ---- 4. O += P V (completes while the next tile's K codes are built) ----
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
@@ -398,21 +470,28 @@ prefill_int8_kernel(const PrefillParams p) {
                            smem_desc(v_addr + 4096 * s, 2048, 128), idesc_o, (j > 0 || s > 0) ? 1u : 0u);
             tc_commit(&sm.bar_o);
         }
-        if (__syncthreads_or(!mbar_wait(&sm.bar_o, phase))) { failed = true; break; }
-        tc_fence_after();
-        phase ^= 1u;
+        pv_pending = true;
     }
+    if (pv_pending) {
+        failed |= !mbar_wait(&sm.bar_o, ph_o);
+        tc_fence_after();
+    }
+    failed = __syncthreads_or(failed);
 
-    // ---- epilogue: O / l, round, rotate by R, round, store ----
+    // ---- epilogue: O / l, round, rotate by R, round, store; this thread's half of the head-dims ----
     if (!failed) {
-        const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        sm.xch[half][row] = l_run;
+        pair_sync(quarter);
+        const float l_all = l_run + sm.xch[half ^ 1][row];
+        const float inv_l = l_all > 0.0f ? 1.0f / l_all : 0.0f;
         T* dst = row_valid ? static_cast<T*>(p.out) + (q_begin + tok) * p.o_stride_tok +
                                  static_cast<int64_t>(kvh * p.G + head_local) * p.o_stride_head
                            : nullptr;
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int c2 = 0; c2 < 2; ++c2) {
+            const int ch = 2 * half + c2;
             uint32_t r[32];
-            tmem_ld32(lane_addr + kPfKeys + 32 * ch, r);
+            tmem_ld32(lane_base + kPfKeys + 32 * ch, r);
             uint32_t outw[16];
 #pragma unroll
             for (int b = 0; b < 8; ++b) {       // rotation block = head-dims 32ch + 4b .. + 3
