@@ -59,6 +59,8 @@ def parse_args():
                     help="override the workload's number of sequences (small cases for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--fused-prefill", action="store_true",
+                    help="prefill workload: the single fused kernel instead of stage + attention")
     return ap.parse_args()
 
 
@@ -555,7 +557,8 @@ def run_prefill_arm(args, w: syn.Workload) -> None:
 
     def attn():
         rq.fused_paged_rq_int8_prefill(q, cache, bt, sl, kc, vc, R, H, D, bs, out=out, cu_seqlens_q=cu,
-                                       max_q_len=T, error_flag=flag)
+                                       max_q_len=T, error_flag=flag, max_seq_len=T,
+                                       staged=not args.fused_prefill)
 
     def step():
         rq.compress_and_store(key, value, cache, slots, R, kb, vb)
@@ -591,8 +594,10 @@ def run_prefill_arm(args, w: syn.Workload) -> None:
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8/bf16",
             "data": "synthetic", "config": workload_config(w, world, B, step=PREFILL_STEP), "clocks": clocks,
-            "gpu_launches": 2 * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "prefill_int8_kernel", "achieved": achieved,
+            "gpu_launches": (2 if args.fused_prefill else 3) * args.steps,
+            "roofline": {"bound": "tensor",
+                         "kernel": "prefill_int8_kernel" if args.fused_prefill
+                         else "prefill_stage_kernel + prefill_attn_kernel", "achieved": achieved,
                          "peak": peak, "peak_kind": f"2 x {kind} bf16 burst (INT8 peak assumed)",
                          "unit": "TOP/s", "frac": achieved / peak, "kernel_ms": attn_ms,
                          "algorithmic_ops": ops, "traffic": None},

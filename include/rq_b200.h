@@ -179,6 +179,28 @@ int rq_prefill_int8(const void* q, void* out, int dtype, int64_t q_stride_tok,
                     int n_centroids_k, const float* centroids_v, int n_centroids_v,
                     const float* rotation, float sm_scale, int* error_flag, void* stream);
 
+/*
+ * rq_prefill_int8 in two steps, for callers that can lend scratch memory: every (sequence, KV head,
+ * 128-key tile) is decompressed once into `workspace` (int8 K codes, key scales, V values, already
+ * in tensor-core operand order) and the attention kernel streams those records with bulk copies
+ * instead of rebuilding them for every block of query rows.  Same results as rq_prefill_int8.
+ *
+ *   max_seq_len      upper bound of seq_lens (host value); sequences longer than it are truncated
+ *   workspace        >= rq_prefill_workspace_bytes(num_seqs, num_kv_heads, max_seq_len) bytes,
+ *                    128-byte aligned; contents are scratch
+ */
+size_t rq_prefill_workspace_bytes(int num_seqs, int num_kv_heads, int max_seq_len);
+int rq_prefill_int8_staged(const void* q, void* out, int dtype, int64_t q_stride_tok,
+                           int64_t q_stride_head, int64_t o_stride_tok, int64_t o_stride_head,
+                           const int32_t* cu_seqlens_q, int num_tokens, int num_seqs, int max_q_len,
+                           int num_q_heads, int num_kv_heads, int head_dim, const uint8_t* kv_cache,
+                           int64_t num_blocks, int block_size, int total_bytes,
+                           const int32_t* block_table, int64_t block_table_stride,
+                           const int32_t* seq_lens, const float* centroids_k, int n_centroids_k,
+                           const float* centroids_v, int n_centroids_v, const float* rotation,
+                           float sm_scale, int* error_flag, int max_seq_len, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

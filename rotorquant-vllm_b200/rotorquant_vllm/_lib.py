@@ -37,6 +37,9 @@ _SIGNATURES = {
                                       _P, _I, _P, _I, _P, _F, _I, _I, _P]),
     "rq_prefill_int8": (_I, [_P, _P, _I, _L, _L, _L, _L, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P,
                              _L, _P, _P, _I, _P, _I, _P, _F, _P, _P]),
+    "rq_prefill_workspace_bytes": (_Z, [_I, _I, _I]),
+    "rq_prefill_int8_staged": (_I, [_P, _P, _I, _L, _L, _L, _L, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P,
+                                    _L, _P, _P, _I, _P, _I, _P, _F, _P, _I, _P, _Z, _P]),
 }
 
 _OPTIONAL: dict = {}

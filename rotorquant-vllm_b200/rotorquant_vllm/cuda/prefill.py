@@ -29,6 +29,9 @@ def fused_paged_rq_int8_prefill(
     cu_seqlens_q: torch.Tensor | None = None,
     max_q_len: int | None = None,
     error_flag: torch.Tensor | None = None,
+    max_seq_len: int | None = None,
+    workspace: torch.Tensor | None = None,
+    staged: bool | None = None,
 ) -> torch.Tensor:
     """Causal attention of ``q (num_tokens, H_Q, D)`` over the compressed paged cache.
 
@@ -36,6 +39,13 @@ def fused_paged_rq_int8_prefill(
     entry (``ValueError`` otherwise, as upstream :305-309).  With ``cu_seqlens_q`` (int32,
     ``num_seqs + 1`` entries) sequence ``s`` owns rows ``cu[s]:cu[s+1]``; in both cases the query
     rows of a sequence are the last rows of its ``seq_lens[s]`` cached tokens.
+
+    Two implementations give the same result: the fused kernel rebuilds the K/V tiles for every
+    block of query rows; the staged one (``rq_prefill_int8_staged``) decompresses every tile once
+    into scratch memory first.  ``staged=None`` picks the staged path when a bound on the sequence
+    lengths is known -- ``max_seq_len``, else the width of the block table -- and the scratch stays
+    under 1 GiB; ``workspace`` (uint8) may supply the scratch, otherwise one buffer per device is
+    kept and grown as needed.
     """
     num_tokens, hq, d = q.shape
     assert d == head_dim
@@ -73,15 +83,42 @@ def fused_paged_rq_int8_prefill(
     ck = k_centroids.to(torch.float32).contiguous()
     cv = v_centroids.to(torch.float32).contiguous()
     seq_lens = seq_lens.contiguous()
+    lib = _lib.lib()
+    bound = int(max_seq_len) if max_seq_len else block_table.shape[1] * block_size
+    need = lib.rq_prefill_workspace_bytes(num_seqs, num_kv_heads, bound)
+    if staged is None:
+        staged = workspace is not None or bool(max_seq_len) or need <= (1 << 30)
+    common = (
+        q.data_ptr(), result.data_ptr(), _lib.dtype_code(q.dtype), q.stride(0), q.stride(1),
+        result.stride(0), result.stride(1),
+        cu_seqlens_q.data_ptr() if cu_seqlens_q is not None else None,
+        num_tokens, num_seqs, int(max_q_len or 0), hq, num_kv_heads, head_dim,
+        kv_cache.data_ptr(), kv_cache.shape[0], block_size, kv_cache.shape[2],
+        block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
+        ck.data_ptr(), ck.numel(), cv.data_ptr(), cv.numel(), rotation.data_ptr(),
+        float(sm_scale), error_flag.data_ptr() if error_flag is not None else None)
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().rq_prefill_int8(
-            q.data_ptr(), result.data_ptr(), _lib.dtype_code(q.dtype), q.stride(0), q.stride(1),
-            result.stride(0), result.stride(1),
-            cu_seqlens_q.data_ptr() if cu_seqlens_q is not None else None,
-            num_tokens, num_seqs, int(max_q_len or 0), hq, num_kv_heads, head_dim,
-            kv_cache.data_ptr(), kv_cache.shape[0], block_size, kv_cache.shape[2],
-            block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
-            ck.data_ptr(), ck.numel(), cv.data_ptr(), cv.numel(), rotation.data_ptr(),
-            float(sm_scale), error_flag.data_ptr() if error_flag is not None else None,
-            _lib.stream_ptr(dev)))
+        if staged:
+            if workspace is None:
+                workspace = _scratch(dev, need)
+            else:
+                _lib.require_cuda(workspace)
+                if workspace.dtype != torch.uint8 or not workspace.is_contiguous():
+                    raise ValueError("workspace must be a contiguous uint8 tensor")
+            _lib.check(lib.rq_prefill_int8_staged(*common, bound, workspace.data_ptr(), workspace.numel(),
+                                                   _lib.stream_ptr(dev)))
+        else:
+            _lib.check(lib.rq_prefill_int8(*common, _lib.stream_ptr(dev)))
     return result
+
+
+_SCRATCH: dict = {}
+
+
+def _scratch(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """One scratch buffer per device for the staged path, grown when a call needs more."""
+    buf = _SCRATCH.get(dev)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        _SCRATCH[dev] = buf
+    return buf

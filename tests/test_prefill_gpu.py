@@ -27,12 +27,13 @@ def _prefill(*a, **k):
     return fused_paged_rq_int8_prefill(*a, **k)
 
 
-def _run(c, cu=None):
+def _run(c, cu=None, staged=None):
+    """staged: False = fused kernel, True = decompress-once scratch + attention kernel, None = launcher's choice."""
     flag = torch.zeros(1, dtype=torch.int32, device=DEV)
     out = _prefill(c["q"].to(DEV), c["kv_cache"].to(DEV), c["block_table"].to(DEV), c["seq_lens"].to(DEV),
                    c["k_centroids"].to(DEV), c["v_centroids"].to(DEV), c["R"].to(DEV), c["num_kv_heads"],
                    128, c["kv_cache"].shape[1], sm_scale=c["sm_scale"],
-                   cu_seqlens_q=None if cu is None else cu.to(DEV), error_flag=flag).cpu()
+                   cu_seqlens_q=None if cu is None else cu.to(DEV), error_flag=flag, staged=staged).cpu()
     assert int(flag.item()) == 0, "a bounded device-side wait expired"
     return out
 
@@ -57,12 +58,13 @@ def _check(out, c, cu):
     assert err.max().item() <= bound and err.mean().item() <= 6e-3, (err.max().item(), err.mean().item())
 
 
+@pytest.mark.parametrize("staged", [False, True])
 @pytest.mark.parametrize("name", helpers.prefill_case_names())
-def test_prefill_golden_cases(name):
+def test_prefill_golden_cases(name, staged):
     c = helpers.load_case(name)
     t = c["q"].shape[0]
     cu = None if t == int(c["seq_lens"][0]) else torch.tensor([0, t], dtype=torch.int32)
-    _check(_run(c, cu), c, cu)
+    _check(_run(c, cu, staged), c, cu)
 
 
 def _fresh(tag, kb, vb, H, HQ, ctx_lens, q_lens, bs, dtype, seed):
@@ -89,9 +91,21 @@ def _fresh(tag, kb, vb, H, HQ, ctx_lens, q_lens, bs, dtype, seed):
     ("iso_fast", 4, 4, 2, 2, [150], [150], 32, torch.float16),                 # G = 1, fp16, block 32
     ("iso_fast", 3, 4, 1, 16, [90, 0, 17], [90, 0, 17], 8, torch.bfloat16),    # G = 16, empty sequence
 ])
-def test_prefill_fresh_cases(tag, kb, vb, H, HQ, ctx, ql, bs, dtype):
+@pytest.mark.parametrize("staged", [False, True])
+def test_prefill_fresh_cases(tag, kb, vb, H, HQ, ctx, ql, bs, dtype, staged):
     c, cu = _fresh(tag, kb, vb, H, HQ, ctx, ql, bs, dtype, seed=H + len(ctx))
-    _check(_run(c, cu), c, cu)
+    _check(_run(c, cu, staged), c, cu)
+
+
+def test_staged_and_fused_prefill_agree_and_workspace_is_checked():
+    c, cu = _fresh("iso_fast", 3, 3, 4, 16, [700, 130], [300, 130], 16, torch.bfloat16, seed=9)
+    a, b = _run(c, cu, False), _run(c, cu, True)
+    assert torch.equal(a, b), (a.float() - b.float()).abs().max().item()
+    g = gpu_util.on_gpu(c)
+    small = torch.empty(1024, dtype=torch.uint8, device=DEV)
+    with pytest.raises(ValueError, match="workspace"):
+        _prefill(g["q"], g["kv_cache"], g["block_table"], g["seq_lens"], g["k_centroids"], g["v_centroids"],
+                 g["R"], 4, 128, 16, cu_seqlens_q=cu.to(DEV), max_seq_len=700, workspace=small)
 
 
 def test_single_sequence_contract():
