@@ -155,6 +155,12 @@ __device__ __forceinline__ uint32_t byte_lookup(const uint32_t* tbl, uint32_t se
     }
 }
 
+// int32 -> float for |x| < 2^22 without the conversion unit (which the exponentials need): adding x
+// to the bit pattern of 1.5 * 2^23 gives the float 1.5 * 2^23 + x exactly.  |Q K^T| <= 128 * 127^2 < 2^21.
+__device__ __forceinline__ float small_int_to_float(uint32_t x) {
+    return __uint_as_float(x + 0x4B400000u) - 12582912.0f;
+}
+
 // Barrier of the two warps that share 32 rows (warp w and w ^ 4): ids 1..4.
 __device__ __forceinline__ void pair_sync(int quarter) {
     asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory");
@@ -227,23 +233,23 @@ prefill_int8_kernel(const PrefillParams p) {
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);   // this warp's TMEM lanes
     const uint32_t core_row_off = (row >> 3) * 1024 + (row & 7) * 16;                // q/k tiles: 8 chunks per row group
 
-    // ---- Q: rotate, round, quantise the row to int8; each of the row's two threads rotates the
-    //      whole row (the scale needs its maximum) and stores its half ----
+    // ---- Q: rotate, round, quantise the row to int8; each of the row's two threads handles half
+    //      of the head-dims (16 rotation blocks, 4 chunks) and they exchange their maxima ----
     float q_scale = 0.0f;
     {
-        uint32_t packed[64];                    // rotated, rounded row as T pairs (d, d+1)
+        uint32_t packed[32];                    // this half of the rotated, rounded row as T pairs (d, d+1)
         float mx = 0.0f;
         if (row_valid) {
             const T* src = static_cast<const T*>(p.q) + (q_begin + tok) * p.q_stride_tok +
-                           static_cast<int64_t>(kvh * p.G + head_local) * p.q_stride_head;
+                           static_cast<int64_t>(kvh * p.G + head_local) * p.q_stride_head + 64 * half;
 #pragma unroll
-            for (int b = 0; b < 32; ++b) {
+            for (int b = 0; b < 16; ++b) {
                 const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src + 4 * b));
                 const float2 x01 = pf_unpack<T>(raw.x), x23 = pf_unpack<T>(raw.y);
                 float r[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float4 rr = *reinterpret_cast<const float4*>(&sm.rot[b * 16 + j * 4]);
+                    const float4 rr = *reinterpret_cast<const float4*>(&sm.rot[(16 * half + b) * 16 + j * 4]);
                     float acc = __fmul_rn(x01.x, rr.x);
                     acc = __fmaf_rn(x01.y, rr.y, acc);
                     acc = __fmaf_rn(x23.x, rr.z, acc);
@@ -257,14 +263,17 @@ prefill_int8_kernel(const PrefillParams p) {
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) packed[i] = 0u;
+            for (int i = 0; i < 32; ++i) packed[i] = 0u;
         }
+        sm.xch[half][row] = mx;
+        pair_sync(quarter);
+        mx = fmaxf(mx, sm.xch[half ^ 1][row]);
+        pair_sync(quarter);                     // xch is reused by the softmax
         const bool ok = mx > 0.0f && mx <= 3.0e38f;
         const float inv = ok ? __fdiv_rn(127.0f, mx) : 0.0f;
         q_scale = ok ? __fdiv_rn(mx, 127.0f) : 0.0f;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {           // 16 head-dims = 16 bytes per chunk
-            if ((c >> 2) != half) continue;
+        for (int c = 0; c < 4; ++c) {           // 16 head-dims = 16 bytes per chunk; chunks 4*half .. 4*half + 3
             uint32_t wds[4];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -274,7 +283,7 @@ prefill_int8_kernel(const PrefillParams p) {
                 // position x holds head-dim x ^ 1
                 wds[w] = (i1 & 0xFF) | ((i0 & 0xFF) << 8) | ((i3 & 0xFF) << 16) | ((i2 & 0xFF) << 24);
             }
-            *reinterpret_cast<uint4*>(&sm.q[core_row_off + c * 128]) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+            *reinterpret_cast<uint4*>(&sm.q[core_row_off + (4 * half + c) * 128]) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
         }
     }
     const float row_factor = q_scale * p.qk_scale;
@@ -387,6 +396,8 @@ prefill_int8_kernel(const PrefillParams p) {
         ph_s ^= 1u;
         tc_fence_after();
 
+        const float* const k_scale = sm.k_scale;
+
         // ---- 3. online softmax: this thread's row, keys 64*half .. 64*half + 63 of the tile ----
         // keys of this half that the row may see: columns 0 .. limit (>= 63: all of them)
         const int limit = pos - (j * kPfKeys + 64 * half);
@@ -394,26 +405,32 @@ prefill_int8_kernel(const PrefillParams p) {
         uint8_t* prow = reinterpret_cast<uint8_t*>(sm.p) + (row >> 3) * (16 * 128) + (row & 7) * 16;
         auto softmax_half = [&](auto masked_tag) {
             constexpr bool kMasked = decltype(masked_tag)::value;
-            // pass A: scale the integer sums by the key scales (kept in TMEM as floats), row maximum
+            // pass A: scale the integer sums by the key scales, row maximum.  The first 32 scaled sums
+            // stay in registers, the other 32 go back to TMEM as floats until pass B.
             float m_half = -INFINITY;
-#pragma unroll 1
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + 64 * half + 32 * ch, r);
+            uint32_t r0[32];
+            auto scale_chunk = [&](uint32_t (&r)[32], int ch) {
 #pragma unroll
                 for (int c4 = 0; c4 < 8; ++c4) {
-                    const float4 ks = *reinterpret_cast<const float4*>(&sm.k_scale[64 * half + 32 * ch + 4 * c4]);
+                    const float4 ks = *reinterpret_cast<const float4*>(&k_scale[64 * half + 32 * ch + 4 * c4]);
                     const float kk[4] = {ks.x, ks.y, ks.z, ks.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int c = 4 * c4 + e;
-                        const float sv = static_cast<float>(static_cast<int>(r[c])) * kk[e];
+                        const float sv = small_int_to_float(r[c]) * kk[e];
                         r[c] = __float_as_uint(sv);
                         if (!kMasked || 32 * ch + c <= limit) m_half = fmaxf(m_half, sv);
                     }
                 }
-                tmem_st32(lane_base + 64 * half + 32 * ch, r);
+            };
+            {
+                uint32_t r1[32];
+                tmem_ld32(lane_base + 64 * half + 32, r1);
+                scale_chunk(r1, 1);
+                tmem_st32(lane_base + 64 * half + 32, r1);
             }
+            tmem_ld32(lane_base + 64 * half, r0);
+            scale_chunk(r0, 0);
             sm.xch[half][row] = m_half;
             pair_sync(quarter);
             const float m_tile = fmaxf(m_half, sm.xch[half ^ 1][row]) * row_factor;     // row_factor >= 0
@@ -435,10 +452,7 @@ prefill_int8_kernel(const PrefillParams p) {
             l_run *= alpha;
             m_run = m_new;
             // pass B: probabilities -> shared P tile (K-major: 16 chunks of 8 keys per row)
-#pragma unroll 1
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + 64 * half + 32 * ch, r);
+            auto emit_chunk = [&](const uint32_t (&r)[32], int ch) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
@@ -455,6 +469,12 @@ prefill_int8_kernel(const PrefillParams p) {
                 for (int kc = 0; kc < 4; ++kc)
                     *reinterpret_cast<uint4*>(prow + (8 * half + 4 * ch + kc) * 128) =
                         make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
+            };
+            emit_chunk(r0, 0);
+            {
+                uint32_t r1[32];
+                tmem_ld32(lane_base + 64 * half + 32, r1);
+                emit_chunk(r1, 1);
             }
         };
         if (unmasked) softmax_half(std::false_type{});
@@ -697,23 +717,23 @@ prefill_attn_kernel(const PrefillParams p) {
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);   // this warp's TMEM lanes
     const uint32_t core_row_off = (row >> 3) * 1024 + (row & 7) * 16;                // q/k tiles: 8 chunks per row group
 
-    // ---- Q: rotate, round, quantise the row to int8; each of the row's two threads rotates the
-    //      whole row (the scale needs its maximum) and stores its half ----
+    // ---- Q: rotate, round, quantise the row to int8; each of the row's two threads handles half
+    //      of the head-dims (16 rotation blocks, 4 chunks) and they exchange their maxima ----
     float q_scale = 0.0f;
     {
-        uint32_t packed[64];                    // rotated, rounded row as T pairs (d, d+1)
+        uint32_t packed[32];                    // this half of the rotated, rounded row as T pairs (d, d+1)
         float mx = 0.0f;
         if (row_valid) {
             const T* src = static_cast<const T*>(p.q) + (q_begin + tok) * p.q_stride_tok +
-                           static_cast<int64_t>(kvh * p.G + head_local) * p.q_stride_head;
+                           static_cast<int64_t>(kvh * p.G + head_local) * p.q_stride_head + 64 * half;
 #pragma unroll
-            for (int b = 0; b < 32; ++b) {
+            for (int b = 0; b < 16; ++b) {
                 const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src + 4 * b));
                 const float2 x01 = pf_unpack<T>(raw.x), x23 = pf_unpack<T>(raw.y);
                 float r[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float4 rr = *reinterpret_cast<const float4*>(&sm.rot[b * 16 + j * 4]);
+                    const float4 rr = *reinterpret_cast<const float4*>(&sm.rot[(16 * half + b) * 16 + j * 4]);
                     float acc = __fmul_rn(x01.x, rr.x);
                     acc = __fmaf_rn(x01.y, rr.y, acc);
                     acc = __fmaf_rn(x23.x, rr.z, acc);
@@ -727,14 +747,17 @@ prefill_attn_kernel(const PrefillParams p) {
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) packed[i] = 0u;
+            for (int i = 0; i < 32; ++i) packed[i] = 0u;
         }
+        sm.xch[half][row] = mx;
+        pair_sync(quarter);
+        mx = fmaxf(mx, sm.xch[half ^ 1][row]);
+        pair_sync(quarter);                     // xch is reused by the softmax
         const bool ok = mx > 0.0f && mx <= 3.0e38f;
         const float inv = ok ? __fdiv_rn(127.0f, mx) : 0.0f;
         q_scale = ok ? __fdiv_rn(mx, 127.0f) : 0.0f;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {           // 16 head-dims = 16 bytes per chunk
-            if ((c >> 2) != half) continue;
+        for (int c = 0; c < 4; ++c) {           // 16 head-dims = 16 bytes per chunk; chunks 4*half .. 4*half + 3
             uint32_t wds[4];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -744,7 +767,7 @@ prefill_attn_kernel(const PrefillParams p) {
                 // position x holds head-dim x ^ 1
                 wds[w] = (i1 & 0xFF) | ((i0 & 0xFF) << 8) | ((i3 & 0xFF) << 16) | ((i2 & 0xFF) << 24);
             }
-            *reinterpret_cast<uint4*>(&sm.q[core_row_off + c * 128]) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+            *reinterpret_cast<uint4*>(&sm.q[core_row_off + (4 * half + c) * 128]) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
         }
     }
     const float row_factor = q_scale * p.qk_scale;
@@ -818,12 +841,11 @@ prefill_attn_kernel(const PrefillParams p) {
         uint8_t* prow = reinterpret_cast<uint8_t*>(sm.p) + (row >> 3) * (16 * 128) + (row & 7) * 16;
         auto softmax_half = [&](auto masked_tag) {
             constexpr bool kMasked = decltype(masked_tag)::value;
-            // pass A: scale the integer sums by the key scales (kept in TMEM as floats), row maximum
+            // pass A: scale the integer sums by the key scales, row maximum.  The first 32 scaled sums
+            // stay in registers, the other 32 go back to TMEM as floats until pass B.
             float m_half = -INFINITY;
-#pragma unroll 1
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + 64 * half + 32 * ch, r);
+            uint32_t r0[32];
+            auto scale_chunk = [&](uint32_t (&r)[32], int ch) {
 #pragma unroll
                 for (int c4 = 0; c4 < 8; ++c4) {
                     const float4 ks = *reinterpret_cast<const float4*>(&k_scale[64 * half + 32 * ch + 4 * c4]);
@@ -831,13 +853,20 @@ prefill_attn_kernel(const PrefillParams p) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int c = 4 * c4 + e;
-                        const float sv = static_cast<float>(static_cast<int>(r[c])) * kk[e];
+                        const float sv = small_int_to_float(r[c]) * kk[e];
                         r[c] = __float_as_uint(sv);
                         if (!kMasked || 32 * ch + c <= limit) m_half = fmaxf(m_half, sv);
                     }
                 }
-                tmem_st32(lane_base + 64 * half + 32 * ch, r);
+            };
+            {
+                uint32_t r1[32];
+                tmem_ld32(lane_base + 64 * half + 32, r1);
+                scale_chunk(r1, 1);
+                tmem_st32(lane_base + 64 * half + 32, r1);
             }
+            tmem_ld32(lane_base + 64 * half, r0);
+            scale_chunk(r0, 0);
             sm.xch[half][row] = m_half;
             pair_sync(quarter);
             const float m_tile = fmaxf(m_half, sm.xch[half ^ 1][row]) * row_factor;     // row_factor >= 0
@@ -859,10 +888,7 @@ prefill_attn_kernel(const PrefillParams p) {
             l_run *= alpha;
             m_run = m_new;
             // pass B: probabilities -> shared P tile (K-major: 16 chunks of 8 keys per row)
-#pragma unroll 1
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + 64 * half + 32 * ch, r);
+            auto emit_chunk = [&](const uint32_t (&r)[32], int ch) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
@@ -879,6 +905,12 @@ prefill_attn_kernel(const PrefillParams p) {
                 for (int kc = 0; kc < 4; ++kc)
                     *reinterpret_cast<uint4*>(prow + (8 * half + 4 * ch + kc) * 128) =
                         make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
+            };
+            emit_chunk(r0, 0);
+            {
+                uint32_t r1[32];
+                tmem_ld32(lane_base + 64 * half + 32, r1);
+                emit_chunk(r1, 1);
             }
         };
         if (unmasked) softmax_half(std::false_type{});
