@@ -77,6 +77,7 @@ struct DecodeParams {
     int64_t o_stride_seq, o_stride_head;
     // streaming kernel
     const int32_t* tile_prefix;           // [num_seqs + 1] exclusive prefix of tiles per sequence
+    const int2* seq_groups;               // [num_seqs] first and last group overlapping the sequence
     int num_seqs;
     int stream_warps;                     // warps of the streaming grid (multiple of 8)
     int stream_groups;                    // groups of J warps; each owns one piece of the tile space
@@ -562,8 +563,10 @@ __device__ __forceinline__ void stream_tile(uint32_t (*tbl_k)[8], uint32_t (*tbl
 }
 
 // Tiles of every sequence as an exclusive prefix sum: prefix[s] = sum_{s' < s} ceil(len[s'] / tile_tokens).
+// Then, for the merge, the first and last group whose piece overlaps each sequence (group g owns the
+// tiles [g * total / groups, (g + 1) * total / groups) of the line of all tiles).
 __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num_seqs, int tile_tokens,
-                                   int32_t* __restrict__ prefix) {
+                                   int32_t* __restrict__ prefix, int groups, int2* __restrict__ seq_groups) {
     __shared__ int warp_sums[32];
     __shared__ int carry;
     if (threadIdx.x == 0) carry = 0;
@@ -587,6 +590,18 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num
         __syncthreads();
     }
     if (threadIdx.x == 0) prefix[num_seqs] = carry;
+    __syncthreads();
+    const int64_t total = carry, ng = groups;
+    for (int s = threadIdx.x; s < num_seqs; s += blockDim.x) {
+        const int64_t a = prefix[s];
+        const int64_t n = (max(__ldg(seq_lens + s), 0) + tile_tokens - 1) / tile_tokens;
+        int2 r = make_int2(0, -1);                                      // empty sequence: no groups
+        if (n > 0) {
+            r.x = static_cast<int>(((a + 1) * ng - 1) / total);        // group holding tile a
+            r.y = static_cast<int>(((a + n) * ng - 1) / total);        // group holding the last tile
+        }
+        seq_groups[s] = r;
+    }
 }
 
 template <typename T, int KB, int VB, bool TMA>
@@ -1236,7 +1251,6 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                     tmem_st16_nowait(lane_base + kUColKhi + 16 * half, hi);
                     tmem_st16_nowait(lane_base + kUColKlo + 16 * half, lo);
                 }
-                tmem_wait_st();
             }
             if constexpr (TMA) {
                 if (tile + 1 < t_end) {                  // the staged rows of the next tile
@@ -1247,6 +1261,7 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             } else {
                 fetch_direct(0, next_slot, kw, nk);
             }
+            tmem_wait_st();                              // the digit planes are in TMEM
             tc_fence_before();
             __syncthreads();
             if (tid == 0) {
@@ -1268,10 +1283,19 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 ph_o ^= 1u;
                 tc_fence_after();
             }
+            uint32_t d[32];                              // the 32 sums of this token (see step 4)
             {
                 const Table<VB> tb = build_value_table<T, VB>(sm.cb[1], nv);
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {       // 8 head-dims = one 32-bit index word per chunk
+                    if (c == 8) {
+                        // S^T is normally complete by now: request this token's sums so that the TMEM
+                        // read runs under the second half of the V row
+                        failed |= !mbar_wait(&sm.bar_s, ph_s);
+                        ph_s ^= 1u;
+                        tc_fence_after();
+                        tmem_ld32_nowait(lane_base + kUColS, d);
+                    }
                     uint32_t lo0, hi0, lo1, hi1;
                     lookup4<VB>(tb, vw[c], lo0, hi0);
                     lookup4<VB>(tb, vw[c] >> 16, lo1, hi1);
@@ -1290,14 +1314,11 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             }
 
             // ---- 4: scores, lazy reference maximum, probabilities ----
-            failed |= !mbar_wait(&sm.bar_s, ph_s);
-            ph_s ^= 1u;
-            tc_fence_after();
             float sc[NH];
             const float tok_bias = valid ? 0.0f : -INFINITY;
             {
-                uint32_t d[32];
-                tmem_ld32(lane_base + kUColS, d);
+                tmem_wait_ld();
+                tmem_ld32_landed(d);
                 const float4 qf0 = *reinterpret_cast<const float4*>(&sm.qf[0]);
                 const float4 qf1 = *reinterpret_cast<const float4*>(&sm.qf[4]);
                 const float qf[8] = {qf0.x, qf0.y, qf0.z, qf0.w, qf1.x, qf1.y, qf1.z, qf1.w};
@@ -1440,20 +1461,19 @@ decode_stream_merge_kernel(const DecodeParams p) {
     const int J = p.H * p.head_groups;
     const int kvh = qh / p.G, hl = qh % p.G;
     const int item = kvh * p.head_groups + hl / kHeadsPerCta, h = hl % kHeadsPerCta;
-    const int pre = __ldg(p.tile_prefix + seq), n_s = __ldg(p.tile_prefix + seq + 1) - pre;
+    const int2 gr = __ldg(p.seq_groups + seq);
     const int64_t total = __ldg(p.tile_prefix + p.num_seqs);
     const int64_t ng = p.stream_groups;
+    const bool n_s = gr.y >= gr.x;                                     // the sequence has tiles
     float acc = 0.0f;
     float l_all = 0.0f;
-    if (n_s > 0) {                                                     // uniform for the CTA
-        const int64_t a = pre, b = a + n_s;                            // the sequence's tiles
-        const int64_t g_first = ((a + 1) * ng - 1) / total;           // group holding tile a
-        const int64_t g_last = (b * ng - 1) / total;                  // group holding tile b - 1
+    if (n_s) {                                                         // uniform for the CTA
+        const int64_t g_first = gr.x, g_last = gr.y;
         float m_all = -INFINITY;
         for (int64_t g0 = g_first; g0 <= g_last; g0 += 32) {           // normally one round
             const int64_t gi = g0 + lane;
-            // groups whose piece is empty (more groups than tiles) wrote nothing
-            const bool live = gi <= g_last && gi * total / ng < (gi + 1) * total / ng;
+            // groups whose piece is empty (only when there are more groups than tiles) wrote nothing
+            const bool live = gi <= g_last && (total >= ng || gi * total / ng < (gi + 1) * total / ng);
             const int64_t r = ((gi + seq) * J + item) * kHeadsPerCta + h;
             if (d < 32) {
                 const float m = live ? p.ws_m[r] : -INFINITY;
@@ -1483,7 +1503,7 @@ decode_stream_merge_kernel(const DecodeParams p) {
             __syncthreads();
         }
     }
-    const float o = n_s > 0 ? acc / l_all : 0.0f;      // an empty sequence yields zeros
+    const float o = n_s ? acc / l_all : 0.0f;          // an empty sequence yields zeros
     o_s[d] = round_to<T>(o);
     __syncthreads();
     // out[j] = sum_k o[k] R[k][j] over the 4x4 block of j, ascending k, fused multiply-adds
@@ -1522,7 +1542,8 @@ static void finish_plan(StreamPlan& pl, long long groups, long long J, int num_s
     pl.groups = static_cast<int>(groups);
     pl.warps = static_cast<int>((groups * J + kDecodeWarps - 1) / kDecodeWarps * kDecodeWarps);
     pl.rows = static_cast<size_t>((groups + num_seqs) * J);
-    pl.prefix_bytes = (static_cast<size_t>(num_seqs + 1) * sizeof(int32_t) + 255) / 256 * 256;
+    // tile prefix sums [num_seqs + 1] (int32, padded to 8 bytes), then the group range of every sequence (int2)
+    pl.prefix_bytes = ((static_cast<size_t>(num_seqs + 2) / 2 * 2) * sizeof(int32_t) + static_cast<size_t>(num_seqs) * sizeof(int2) + 255) / 256 * 256;
     pl.bytes = pl.prefix_bytes + pl.rows * kHeadsPerCta * (kHeadDim + 2) * sizeof(float);
 }
 // Streaming kernel: groups get at least 8 tiles of 16 tokens each when the bound on the work
@@ -1623,7 +1644,8 @@ template <typename T, int KB, int VB>
 static int launch_decode(const DecodeParams& p, int num_seqs, cudaStream_t st) {
     const bool umma = decode_path() == DecodePath::kUmma;
     decode_plan_kernel<<<1, 1024, 0, st>>>(p.seq_lens, num_seqs, umma ? kUTile : kTile,
-                                           const_cast<int32_t*>(p.tile_prefix));
+                                           const_cast<int32_t*>(p.tile_prefix), p.stream_groups,
+                                           const_cast<int2*>(p.seq_groups));
     if (int e = check_cuda(cudaGetLastError(), "rq_decode plan launch")) return e;
     alignas(64) CUtensorMap map_idx{}, map_norm{};
     bool tma = tma_eligible(p);
@@ -1726,6 +1748,7 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
     p.qk_scale = sm_scale * 1.4426950408889634f;
     p.H = num_kv_heads; p.Hq = num_q_heads; p.G = G; p.head_groups = head_groups;
     p.tile_prefix = static_cast<const int32_t*>(workspace);
+    p.seq_groups = reinterpret_cast<const int2*>(static_cast<const int32_t*>(workspace) + (num_seqs + 2) / 2 * 2);
     const size_t rows = pl.rows * kHeadsPerCta;
     p.ws_o = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.prefix_bytes);
     p.ws_m = p.ws_o + rows * kHeadDim;
