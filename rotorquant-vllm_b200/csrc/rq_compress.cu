@@ -25,6 +25,7 @@ namespace rq {
 
 constexpr int kCompressThreads = 256;                 // 16 rows per CTA
 constexpr int kRowsPerCta = kCompressThreads / 16;
+constexpr int kCompressGrid = 148 * 4;                // the grid walks the rows: at most 4 CTAs per SM
 
 struct CompressParams {
     const void* src[2];          // key, value (or x, unused)
@@ -45,25 +46,8 @@ struct CompressParams {
     const float* rotation;       // dense 128x128
     const float* bounds[2];
     int n_bounds[2];
+    int h_shift;                 // log2(H) when H is a power of two, else -1
 };
-
-struct CompressSmem {
-    float rot[32 * 16];                          // [block][out j][in k]
-    float bnd[2][16];                            // K and V boundaries, padded with +inf
-    float sq[kRowsPerCta][16][8];                // squares of every row, [thread c][lane l]
-};
-
-__device__ __forceinline__ void load_params(const CompressParams& p, CompressSmem& sm) {
-    for (int i = threadIdx.x; i < 32 * 16; i += blockDim.x) {
-        const int g = i >> 4, j = (i >> 2) & 3, k = i & 3;
-        sm.rot[i] = __ldg(p.rotation + (4 * g + j) * kHeadDim + 4 * g + k);
-    }
-    if (threadIdx.x < 32) {
-        const int kv = threadIdx.x >> 4, b = threadIdx.x & 15;
-        sm.bnd[kv][b] = (p.bounds[kv] != nullptr && b < p.n_bounds[kv])
-                            ? __ldg(p.bounds[kv] + b) : __int_as_float(0x7f800000);
-    }
-}
 
 // Eight consecutive elements of a row as fp32.
 template <typename T>
@@ -76,28 +60,65 @@ __device__ __forceinline__ void load8(const T* src, float* x) {
     }
 }
 
-// Normalise, rotate and bucketize this thread's two 4-wide blocks; NB boundaries kept in registers.
-template <int NB>
-__device__ __forceinline__ uint32_t quantize_chunk(const float (&x)[8], int j, float denom,
-                                                   const CompressSmem& sm,
-                                                   const float* __restrict__ bnd) {
-    float bd[NB];
+// What a thread keeps for the whole launch: the two 4x4 rotation blocks of its elements
+// (thread j of a row owns blocks 2j and 2j+1), as rot[half][out jj][in k].
+struct ThreadRotation {
+    float r[32];
+};
+__device__ __forceinline__ ThreadRotation load_rotation(const float* __restrict__ rotation, int j) {
+    ThreadRotation t;
 #pragma unroll
-    for (int b = 0; b < NB; ++b) bd[b] = bnd[b];
+    for (int i = 0; i < 32; ++i) {
+        const int g = 2 * j + (i >> 4), jj = (i >> 2) & 3, k = i & 3;
+        t.r[i] = __ldg(rotation + (4 * g + jj) * kHeadDim + 4 * g + k);          // R[4g+jj][4g+k]
+    }
+    return t;
+}
+
+// The 16 threads of a row: returns this thread's packed word (8 indices) and the row norm.
+// `x` are the thread's elements 8j..8j+7, `sq_row` the row's [16][8] exchange area in shared
+// memory, `bd` the NB boundaries; all 32 lanes of the warp must call this.
+template <int NB>
+__device__ __forceinline__ uint32_t compress_chunk(const float (&x)[8], int j, float* sq_row,
+                                                   const ThreadRotation& rot, const float (&bd)[NB],
+                                                   float& norm_out) {
+    // squares, published for the in-order lane sums
+    float* mine = sq_row + 8 * j;
+    *reinterpret_cast<float4*>(mine) = make_float4(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]),
+                                                   __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
+    *reinterpret_cast<float4*>(mine + 4) = make_float4(__fmul_rn(x[4], x[4]), __fmul_rn(x[5], x[5]),
+                                                       __fmul_rn(x[6], x[6]), __fmul_rn(x[7], x[7]));
+    __syncwarp();
+    float s = 0.0f;
+    if (j < 8) {
+        float v[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] = sq_row[8 * c + j];
+        s = v[0];
+#pragma unroll
+        for (int c = 1; c < 16; ++c) s = __fadd_rn(s, v[c]);
+    }
+    float tot = __shfl_sync(0xffffffffu, s, 0, 16);
+#pragma unroll
+    for (int l = 1; l < 8; ++l) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, s, l, 16));
+    __syncwarp();                                   // sq_row may be rewritten by the next row
+    const float norm = __fsqrt_rn(tot);
+    norm_out = norm;
+    const float denom = __fadd_rn(norm, 1e-10f);
+
     uint32_t word = 0;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-        const int g = 2 * j + half;
         const float x0 = __fdiv_rn(x[4 * half], denom), x1 = __fdiv_rn(x[4 * half + 1], denom);
         const float x2 = __fdiv_rn(x[4 * half + 2], denom), x3 = __fdiv_rn(x[4 * half + 3], denom);
         uint32_t idx[4];
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-            const float4 r = *reinterpret_cast<const float4*>(sm.rot + g * 16 + jj * 4);
-            float acc = __fmul_rn(x0, r.x);
-            acc = __fmaf_rn(x1, r.y, acc);
-            acc = __fmaf_rn(x2, r.z, acc);
-            acc = __fmaf_rn(x3, r.w, acc);
+            const float* r = &rot.r[16 * half + 4 * jj];
+            float acc = __fmul_rn(x0, r[0]);
+            acc = __fmaf_rn(x1, r[1], acc);
+            acc = __fmaf_rn(x2, r[2], acc);
+            acc = __fmaf_rn(x3, r[3], acc);
             uint32_t n = 0;
 #pragma unroll
             for (int b = 0; b < NB; ++b) n += (bd[b] < acc) ? 1u : 0u;
@@ -110,90 +131,104 @@ __device__ __forceinline__ uint32_t quantize_chunk(const float (&x)[8], int j, f
     return word;
 }
 
-// The 16 threads of a row: returns this thread's packed word (8 indices) and the row norm.
-// `x` are the thread's elements 8j..8j+7; all 32 lanes of the warp must call this.
-__device__ __forceinline__ uint32_t compress_chunk(const float (&x)[8], int row_in_cta, int j,
-                                                   CompressSmem& sm, const float* __restrict__ bnd,
-                                                   int nb, float& norm_out) {
-    // squares, published for the in-order lane sums
-    float* mine = sm.sq[row_in_cta][j];
-    *reinterpret_cast<float4*>(mine) = make_float4(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]),
-                                                   __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
-    *reinterpret_cast<float4*>(mine + 4) = make_float4(__fmul_rn(x[4], x[4]), __fmul_rn(x[5], x[5]),
-                                                       __fmul_rn(x[6], x[6]), __fmul_rn(x[7], x[7]));
-    __syncwarp();
-    float s = 0.0f;
-    if (j < 8) {
-        s = sm.sq[row_in_cta][0][j];
+// Store variant.  A fixed grid walks the rows: first all K rows (token-major, head-minor), then
+// all V rows, two rows per warp per step, the next rows' elements loaded while the current ones
+// are processed.  Every row's 16 threads write its 64 index bytes and its norm straight into the
+// token's cache slot; the K row of head 0 also zeroes the slot's padding.
+template <typename T, int NB>
+__device__ __forceinline__ void store_rows(const CompressParams& p, int kv, const ThreadRotation& rot,
+                                           float* sq_row, int j) {
+    float bd[NB];
 #pragma unroll
-        for (int c = 1; c < 16; ++c) s = __fadd_rn(s, sm.sq[row_in_cta][c][j]);
+    for (int b = 0; b < NB; ++b) bd[b] = __ldg(p.bounds[kv] + b);
+    const int H = p.H;
+    const SlotLayout lay = slot_layout(H);
+    const uint32_t rows = static_cast<uint32_t>(p.num_tokens) * static_cast<uint32_t>(H);
+    const uint32_t step = gridDim.x * kRowsPerCta;
+    const uint32_t first = blockIdx.x * kRowsPerCta + (threadIdx.x >> 4);
+    const T* src = static_cast<const T*>(p.src[kv]);
+    auto locate = [&](uint32_t r, uint32_t& token, uint32_t& h) {
+        if (p.h_shift >= 0) { token = r >> p.h_shift; h = r & (H - 1); }
+        else { token = r / H; h = r - token * H; }
+    };
+    auto fetch = [&](uint32_t r, float (&x)[8]) {
+        uint32_t token, h;
+        locate(r < rows ? r : 0u, token, h);        // rows past the end compute on row 0 and store nothing
+        load8<T>(src + token * p.token_stride[kv] + static_cast<int64_t>(h) * p.head_stride[kv] + 8 * j, x);
+    };
+    float x[8], nx[8];
+    // the two rows of a warp run in lock step (shuffles, __syncwarp): loop on the warp's first row
+    const uint32_t warp_first = first & ~1u;
+    if (warp_first < rows) fetch(first, x);
+    for (uint32_t wr = warp_first, r = first; wr < rows; wr += step, r += step) {
+        if (wr + step < rows) fetch(r + step, nx);
+        float norm;
+        const uint32_t word = compress_chunk<NB>(x, j, sq_row, rot, bd, norm);
+        if (r < rows) {
+            uint32_t token, h;
+            locate(r, token, h);
+            const int64_t slot = __ldg(p.slot_mapping + token);
+            if (slot >= 0 && slot < p.num_slots) {
+                uint8_t* dst = p.cache + slot * p.total_bytes;
+                *reinterpret_cast<uint32_t*>(dst + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim + 4 * j) = word;
+                if (j == 0) *reinterpret_cast<float*>(dst + (kv ? lay.v_norm : lay.k_norm) + 4 * h) = norm;
+                if (p.write_padding && kv == 0 && h == 0) {
+                    const int units = (lay.total - lay.payload_end) / 8;
+                    for (int u = j; u < units; u += 16)
+                        *reinterpret_cast<uint2*>(dst + lay.payload_end + 8 * u) = make_uint2(0u, 0u);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = nx[i];
     }
-    float tot = __shfl_sync(0xffffffffu, s, 0, 16);
-#pragma unroll
-    for (int l = 1; l < 8; ++l) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, s, l, 16));
-    const float norm = __fsqrt_rn(tot);
-    norm_out = norm;
-    const float denom = __fadd_rn(norm, 1e-10f);
-
-    return nb <= 7 ? quantize_chunk<7>(x, j, denom, sm, bnd) : quantize_chunk<15>(x, j, denom, sm, bnd);
 }
 
-// Store variant: rows are ordered (K|V, token, head) so that the two rows of a warp normally use
-// the same codebook; every row's 16 threads write its 64 index bytes and its norm straight into
-// the token's cache slot, and the K row of head 0 also zeroes the slot's padding.
 template <typename T>
 __global__ void __launch_bounds__(kCompressThreads)
 compress_store_kernel(const CompressParams p) {
-    __shared__ CompressSmem sm;
-    load_params(p, sm);
-    __syncthreads();
-    const int H = p.H;
-    const SlotLayout lay = slot_layout(H);
-    const int64_t rows_per_kind = p.num_tokens * H;
-    const int row_in_cta = threadIdx.x >> 4, j = threadIdx.x & 15;
-    const int64_t r = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + row_in_cta;
-    const bool live = r < 2 * rows_per_kind;
-    const int64_t rr = live ? r : 0;           // dead rows compute on row 0 and store nothing
-    const int kv = static_cast<int>(rr / rows_per_kind);
-    const int64_t rem = rr % rows_per_kind;
-    const int64_t token = rem / H;
-    const int h = static_cast<int>(rem % H);
+    __shared__ __align__(16) float sq[kRowsPerCta][16 * 8];
+    const int j = threadIdx.x & 15;
+    const ThreadRotation rot = load_rotation(p.rotation, j);
+    float* sq_row = sq[threadIdx.x >> 4];
+#pragma unroll 1
+    for (int kv = 0; kv < 2; ++kv) {
+        if (p.n_bounds[kv] <= 7) store_rows<T, 7>(p, kv, rot, sq_row, j);
+        else store_rows<T, 15>(p, kv, rot, sq_row, j);
+    }
+}
 
-    float x[8];
-    load8<T>(static_cast<const T*>(p.src[kv]) + token * p.token_stride[kv] +
-                 static_cast<int64_t>(h) * p.head_stride[kv] + 8 * j, x);
-    float norm;
-    const uint32_t word = compress_chunk(x, row_in_cta, j, sm, sm.bnd[kv], p.n_bounds[kv], norm);
-    if (!live) return;
-    const int64_t slot = __ldg(p.slot_mapping + token);
-    if (slot < 0 || slot >= p.num_slots) return;
-    uint8_t* dst = p.cache + slot * p.total_bytes;
-    *reinterpret_cast<uint32_t*>(dst + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim + 4 * j) = word;
-    if (j == 0) *reinterpret_cast<float*>(dst + (kv ? lay.v_norm : lay.k_norm) + 4 * h) = norm;
-    if (p.write_padding && kv == 0 && h == 0) {
-        const int units = (lay.total - lay.payload_end) / 8;
-        for (int u = j; u < units; u += 16)
-            *reinterpret_cast<uint2*>(dst + lay.payload_end + 8 * u) = make_uint2(0u, 0u);
+// Rows variant: x (rows, 128) -> packed (rows, 64) + norms, same walk.
+template <typename T, int NB>
+__device__ __forceinline__ void plain_rows(const CompressParams& p, const ThreadRotation& rot, float* sq_row, int j) {
+    float bd[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) bd[b] = __ldg(p.bounds[0] + b);
+    const int64_t rows = p.num_tokens;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * kRowsPerCta;
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + (threadIdx.x >> 4);
+    const T* src = static_cast<const T*>(p.src[0]);
+    for (int64_t wr = first & ~1ll, r = first; wr < rows; wr += step, r += step) {
+        float x[8];
+        load8<T>(src + (r < rows ? r : 0) * p.token_stride[0] + 8 * j, x);
+        float norm;
+        const uint32_t word = compress_chunk<NB>(x, j, sq_row, rot, bd, norm);
+        if (r < rows) {
+            reinterpret_cast<uint32_t*>(p.packed_out + r * kHalfDim)[j] = word;
+            if (j == 0) p.norms_out[r] = norm;
+        }
     }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kCompressThreads)
 compress_rows_kernel(const CompressParams p) {
-    __shared__ CompressSmem sm;
-    load_params(p, sm);
-    __syncthreads();
-    const int row_in_cta = threadIdx.x >> 4, j = threadIdx.x & 15;
-    const int64_t r = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + row_in_cta;
-    const bool live = r < p.num_tokens;
-    const int64_t rr = live ? r : 0;
-    float x[8];
-    load8<T>(static_cast<const T*>(p.src[0]) + rr * p.token_stride[0] + 8 * j, x);
-    float norm;
-    const uint32_t word = compress_chunk(x, row_in_cta, j, sm, sm.bnd[0], p.n_bounds[0], norm);
-    if (!live) return;
-    reinterpret_cast<uint32_t*>(p.packed_out + r * kHalfDim)[j] = word;
-    if (j == 0) p.norms_out[r] = norm;
+    __shared__ __align__(16) float sq[kRowsPerCta][16 * 8];
+    const int j = threadIdx.x & 15;
+    const ThreadRotation rot = load_rotation(p.rotation, j);
+    float* sq_row = sq[threadIdx.x >> 4];
+    if (p.n_bounds[0] <= 7) plain_rows<T, 7>(p, rot, sq_row, j);
+    else plain_rows<T, 15>(p, rot, sq_row, j);
 }
 
 // ---- decompress ------------------------------------------------------------
@@ -257,13 +292,15 @@ static int check_bounds_count(int n, const char* what) {
 
 template <typename T>
 static void launch_store(const CompressParams& p, cudaStream_t st) {
-    const int64_t rows = 2 * p.num_tokens * p.H;
-    const unsigned grid = static_cast<unsigned>((rows + kRowsPerCta - 1) / kRowsPerCta);
+    const int64_t rows = p.num_tokens * p.H;                               // per kind
+    const int64_t want = (rows + kRowsPerCta - 1) / kRowsPerCta;
+    const unsigned grid = static_cast<unsigned>(want < kCompressGrid ? want : kCompressGrid);
     compress_store_kernel<T><<<grid, kCompressThreads, 0, st>>>(p);
 }
 template <typename T>
 static void launch_rows(const CompressParams& p, cudaStream_t st) {
-    const unsigned grid = static_cast<unsigned>((p.num_tokens + kRowsPerCta - 1) / kRowsPerCta);
+    const int64_t want = (p.num_tokens + kRowsPerCta - 1) / kRowsPerCta;
+    const unsigned grid = static_cast<unsigned>(want < kCompressGrid ? want : kCompressGrid);
     compress_rows_kernel<T><<<grid, kCompressThreads, 0, st>>>(p);
 }
 
@@ -301,7 +338,7 @@ extern "C" int rq_compress_store(const void* key, const void* value, int in_dtyp
                         static_cast<long long>(s));
     if (!aligned(key, 16) || !aligned(value, 16) || !aligned(kv_cache, 16))
         return fail(RQ_ERR_ALIGNMENT, "rq_compress_store: key/value/kv_cache must be 16-byte aligned");
-    if (2 * num_tokens * num_kv_heads / kRowsPerCta >= 0x7fffffffLL)
+    if (num_tokens * num_kv_heads >= 0x3fffffffLL)
         return fail(RQ_ERR_UNSUPPORTED, "rq_compress_store: too many rows for one launch");
 
     CompressParams p{};
@@ -309,6 +346,9 @@ extern "C" int rq_compress_store(const void* key, const void* value, int in_dtyp
     p.token_stride[0] = k_token_stride; p.token_stride[1] = v_token_stride;
     p.head_stride[0] = k_head_stride; p.head_stride[1] = v_head_stride;
     p.num_tokens = num_tokens; p.H = num_kv_heads;
+    p.h_shift = -1;
+    for (int sft = 0; sft < 16; ++sft)
+        if ((1 << sft) == num_kv_heads) p.h_shift = sft;
     p.cache = kv_cache; p.num_slots = num_slots; p.total_bytes = total_bytes;
     p.slot_mapping = slot_mapping; p.write_padding = write_padding;
     p.rotation = rotation;
