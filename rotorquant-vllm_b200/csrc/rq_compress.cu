@@ -75,6 +75,32 @@ __device__ __forceinline__ ThreadRotation load_rotation(const float* __restrict_
     return t;
 }
 
+// Number of boundaries strictly below v.  The boundaries ascend, so "bd[b] < v" is true for a
+// prefix of them and a binary search over that prefix gives the count with log2(NB + 1) compares
+// (a NaN compares false everywhere: 0, as the linear count gives).
+template <int NB>
+__device__ __forceinline__ uint32_t count_below(const float (&bd)[NB], float v) {
+    if constexpr (NB == 7) {
+        const bool c1 = bd[3] < v;
+        const bool c2 = (c1 ? bd[5] : bd[1]) < v;
+        const float lo = c2 ? bd[2] : bd[0], hi = c2 ? bd[6] : bd[4];
+        const bool c3 = (c1 ? hi : lo) < v;
+        return (c1 ? 4u : 0u) + (c2 ? 2u : 0u) + (c3 ? 1u : 0u);
+    } else {
+        static_assert(NB == 15, "7 or 15 boundaries");
+        const bool c1 = bd[7] < v;
+        const bool c2 = (c1 ? bd[11] : bd[3]) < v;
+        const float m3a = c2 ? bd[5] : bd[1], m3b = c2 ? bd[13] : bd[9];
+        const bool c3 = (c1 ? m3b : m3a) < v;
+        // fourth level: boundary 8*c1 + 4*c2 + 2*c3
+        const float q0 = c3 ? bd[2] : bd[0], q1 = c3 ? bd[6] : bd[4];
+        const float q2 = c3 ? bd[10] : bd[8], q3 = c3 ? bd[14] : bd[12];
+        const float h0 = c2 ? q1 : q0, h1 = c2 ? q3 : q2;
+        const bool c4 = (c1 ? h1 : h0) < v;
+        return (c1 ? 8u : 0u) + (c2 ? 4u : 0u) + (c3 ? 2u : 0u) + (c4 ? 1u : 0u);
+    }
+}
+
 // The 16 threads of a row: returns this thread's packed word (8 indices) and the row norm.
 // `x` are the thread's elements 8j..8j+7, `sq_row` the row's [16][8] exchange area in shared
 // memory, `bd` the NB boundaries; all 32 lanes of the warp must call this.
@@ -119,10 +145,7 @@ __device__ __forceinline__ uint32_t compress_chunk(const float (&x)[8], int j, f
             acc = __fmaf_rn(x1, r[1], acc);
             acc = __fmaf_rn(x2, r[2], acc);
             acc = __fmaf_rn(x3, r[3], acc);
-            uint32_t n = 0;
-#pragma unroll
-            for (int b = 0; b < NB; ++b) n += (bd[b] < acc) ? 1u : 0u;
-            idx[jj] = n;
+            idx[jj] = count_below<NB>(bd, acc);
         }
         const uint32_t b0 = (idx[0] << 4) | idx[1];
         const uint32_t b1 = (idx[2] << 4) | idx[3];
@@ -151,23 +174,24 @@ __device__ __forceinline__ void store_rows(const CompressParams& p, int kv, cons
         if (p.h_shift >= 0) { token = r >> p.h_shift; h = r & (H - 1); }
         else { token = r / H; h = r - token * H; }
     };
-    auto fetch = [&](uint32_t r, float (&x)[8]) {
+    auto fetch = [&](uint32_t r, float (&x)[8], int64_t& slot) {
         uint32_t token, h;
         locate(r < rows ? r : 0u, token, h);        // rows past the end compute on row 0 and store nothing
         load8<T>(src + token * p.token_stride[kv] + static_cast<int64_t>(h) * p.head_stride[kv] + 8 * j, x);
+        slot = __ldg(p.slot_mapping + token);
     };
     float x[8], nx[8];
+    int64_t slot = -1, nslot = -1;
     // the two rows of a warp run in lock step (shuffles, __syncwarp): loop on the warp's first row
     const uint32_t warp_first = first & ~1u;
-    if (warp_first < rows) fetch(first, x);
+    if (warp_first < rows) fetch(first, x, slot);
     for (uint32_t wr = warp_first, r = first; wr < rows; wr += step, r += step) {
-        if (wr + step < rows) fetch(r + step, nx);
+        if (wr + step < rows) fetch(r + step, nx, nslot);
         float norm;
         const uint32_t word = compress_chunk<NB>(x, j, sq_row, rot, bd, norm);
         if (r < rows) {
             uint32_t token, h;
             locate(r, token, h);
-            const int64_t slot = __ldg(p.slot_mapping + token);
             if (slot >= 0 && slot < p.num_slots) {
                 uint8_t* dst = p.cache + slot * p.total_bytes;
                 *reinterpret_cast<uint32_t*>(dst + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim + 4 * j) = word;
@@ -181,6 +205,7 @@ __device__ __forceinline__ void store_rows(const CompressParams& p, int kv, cons
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = nx[i];
+        slot = nslot;
     }
 }
 
