@@ -49,6 +49,29 @@ struct CompressParams {
     int h_shift;                 // log2(H) when H is a power of two, else -1
 };
 
+// Eight consecutive elements of a row, raw (converted only when they are used, so that a load
+// issued ahead of time does not make its issuer wait).
+template <typename T>
+struct Raw8 {
+    uint4 a, b;               // b only for 4-byte elements
+};
+template <typename T>
+__device__ __forceinline__ Raw8<T> load_raw8(const T* src) {
+    Raw8<T> r;
+    r.a = __ldg(reinterpret_cast<const uint4*>(src));
+    if constexpr (sizeof(T) == 4) r.b = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ void unpack8(const Raw8<T>& r, float* x) {
+    if constexpr (sizeof(T) == 4) {
+        Chunk16<float>::unpack(r.a, x);
+        Chunk16<float>::unpack(r.b, x + 4);
+    } else {
+        Chunk16<T>::unpack(r.a, x);
+    }
+}
+
 // Eight consecutive elements of a row as fp32.
 template <typename T>
 __device__ __forceinline__ void load8(const T* src, float* x) {
@@ -174,19 +197,21 @@ __device__ __forceinline__ void store_rows(const CompressParams& p, int kv, cons
         if (p.h_shift >= 0) { token = r >> p.h_shift; h = r & (H - 1); }
         else { token = r / H; h = r - token * H; }
     };
-    auto fetch = [&](uint32_t r, float (&x)[8], int64_t& slot) {
+    auto fetch = [&](uint32_t r, Raw8<T>& raw, int64_t& slot) {
         uint32_t token, h;
         locate(r < rows ? r : 0u, token, h);        // rows past the end compute on row 0 and store nothing
-        load8<T>(src + token * p.token_stride[kv] + static_cast<int64_t>(h) * p.head_stride[kv] + 8 * j, x);
+        raw = load_raw8<T>(src + token * p.token_stride[kv] + static_cast<int64_t>(h) * p.head_stride[kv] + 8 * j);
         slot = __ldg(p.slot_mapping + token);
     };
-    float x[8], nx[8];
+    Raw8<T> raw{}, nraw{};
     int64_t slot = -1, nslot = -1;
     // the two rows of a warp run in lock step (shuffles, __syncwarp): loop on the warp's first row
     const uint32_t warp_first = first & ~1u;
-    if (warp_first < rows) fetch(first, x, slot);
+    if (warp_first < rows) fetch(first, raw, slot);
     for (uint32_t wr = warp_first, r = first; wr < rows; wr += step, r += step) {
-        if (wr + step < rows) fetch(r + step, nx, nslot);
+        if (wr + step < rows) fetch(r + step, nraw, nslot);
+        float x[8];
+        unpack8<T>(raw, x);
         float norm;
         const uint32_t word = compress_chunk<NB>(x, j, sq_row, rot, bd, norm);
         if (r < rows) {
@@ -203,8 +228,7 @@ __device__ __forceinline__ void store_rows(const CompressParams& p, int kv, cons
                 }
             }
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = nx[i];
+        raw = nraw;
         slot = nslot;
     }
 }
