@@ -37,19 +37,10 @@
 
 namespace rq {
 
-#ifndef RQ_X_WARPS
-#define RQ_X_WARPS 8
-#endif
-#ifndef RQ_X_STAGES
-#define RQ_X_STAGES 3
-#endif
-#ifndef RQ_X_VFIRST
-#define RQ_X_VFIRST 0
-#endif
-constexpr int kDecodeWarps = RQ_X_WARPS;
+constexpr int kDecodeWarps = 8;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kTile = 16;                 // tokens per tile (one mma k-step of P@V)
-constexpr int kStages = RQ_X_STAGES;                // cp.async ring depth per warp
+constexpr int kStages = 3;                // cp.async ring depth per warp
 constexpr int kVPitch = 80;               // bytes per token row of V indices in smem (64 + pad)
 constexpr int kHeadsPerCta = 8;           // query heads handled per CTA (mma N of P@V)
 
@@ -463,8 +454,6 @@ __device__ __forceinline__ void stream_tile(uint32_t (*tbl_k)[8], uint32_t (*tbl
         }
     };
 
-    if (RQ_X_VFIRST) dequant_v();
-
     // ---- S = Q K^T on the int8 path: rows = heads (g), columns = tokens ----
     // acc_h = [Qhi; Qlo] . Khi, acc_l = [Qhi; Qlo] . Klo: entries 0,1 are the Qhi rows, entries
     // 2,3 the Qlo rows of the same head and the same two tokens.  The two token groups (nt) run
@@ -549,7 +538,7 @@ __device__ __forceinline__ void stream_tile(uint32_t (*tbl_k)[8], uint32_t (*tbl
     const uint32_t pl0 = pack_pair<T>(pr[0] - h0.x, pr[1] - h0.y);
     const uint32_t pl1 = pack_pair<T>(pr[2] - h1.x, pr[3] - h1.y);
 
-    if (!RQ_X_VFIRST) dequant_v();
+    dequant_v();
     __syncwarp();
 
     // ---- O^T += V^T P^T : rows = 16 head-dim positions per m-tile, columns = heads ----
