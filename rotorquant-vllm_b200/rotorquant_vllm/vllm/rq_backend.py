@@ -355,6 +355,11 @@ class RQAttentionImpl(FlashAttentionImpl):
         extra = {}
         if num_seqs != 1:
             extra["cu_seqlens_q"] = attn_metadata.query_start_loc
+        # host-side bounds from the metadata: they size the grid and the scratch of the staged path
+        if getattr(attn_metadata, "max_query_len", None):
+            extra["max_q_len"] = int(attn_metadata.max_query_len)
+        if getattr(attn_metadata, "max_seq_len", None):
+            extra["max_seq_len"] = int(attn_metadata.max_seq_len)
         _fused_paged_rq_int8_prefill_fn(query[:n], *common, sm_scale=self.scale, out=output[:n],
                                         **extra)
         return output

@@ -203,7 +203,11 @@ def test_multi_sequence_prefill_passes_query_start_loc(monkeypatch):
                          seq_lens=torch.tensor([4, 20], dtype=torch.int32))
     impl.forward(None, query, None, None, torch.zeros(4, 16, 2048, dtype=torch.uint8), md,
                  output=torch.zeros_like(query))
-    assert log[0]["extra"] == ["cu_seqlens_q"]
+    assert log[0]["extra"] == ["cu_seqlens_q", "max_q_len"]
+    md.max_seq_len = 20
+    impl.forward(None, query, None, None, torch.zeros(4, 16, 2048, dtype=torch.uint8), md,
+                 output=torch.zeros_like(query))
+    assert log[1]["extra"] == ["cu_seqlens_q", "max_q_len", "max_seq_len"]
 
 
 def test_forward_edge_cases(monkeypatch):
