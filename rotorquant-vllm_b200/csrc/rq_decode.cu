@@ -1324,6 +1324,26 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             bool grow = false;
 #pragma unroll
             for (int h = 0; h < NH; ++h) grow |= sc[h] > m_ref[h] + 8.0f;
+            // The probabilities are written on the assumption that no reference maximum moves; the
+            // block votes at the barrier that the P V issue needs anyway, and in the rare other case
+            // the maxima are moved and the probabilities written again.
+            float pr[NH];
+            auto emit_p = [&]() {
+#pragma unroll
+                for (int h = 0; h < NH; ++h) pr[h] = ex2_approx(sc[h] - m_ref[h]);
+                uint32_t ph[4] = {0u, 0u, 0u, 0u}, pl[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                for (int j = 0; j < NH / 2; ++j) {
+                    ph[j] = pack_pair<T>(pr[2 * j], pr[2 * j + 1]);
+                    const float2 back = unpack_pair<T>(ph[j]);
+                    pl[j] = pack_pair<T>(pr[2 * j] - back.x, pr[2 * j + 1] - back.y);
+                }
+                *reinterpret_cast<uint4*>(p_dst) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                *reinterpret_cast<uint4*>(p_dst + 128) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                fence_async_proxy();
+                tc_fence_before();
+            };
+            emit_p();
             if (__syncthreads_or(grow || failed)) {
                 if (__syncthreads_or(failed)) { dead = true; break; }
                 // move the reference maxima: CTA-wide maximum per head, rescale sums and O^T
@@ -1355,27 +1375,11 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                     tmem_st16_nowait(lane_base + kUColO, o);
                     tmem_wait_st();
                 }
+                emit_p();
+                __syncthreads();
             }
-            {
-                float pr[NH];
 #pragma unroll
-                for (int h = 0; h < NH; ++h) {
-                    pr[h] = ex2_approx(sc[h] - m_ref[h]);
-                    l_acc[h] += pr[h];
-                }
-                uint32_t ph[4] = {0u, 0u, 0u, 0u}, pl[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-                for (int j = 0; j < NH / 2; ++j) {
-                    ph[j] = pack_pair<T>(pr[2 * j], pr[2 * j + 1]);
-                    const float2 back = unpack_pair<T>(ph[j]);
-                    pl[j] = pack_pair<T>(pr[2 * j] - back.x, pr[2 * j + 1] - back.y);
-                }
-                *reinterpret_cast<uint4*>(p_dst) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                *reinterpret_cast<uint4*>(p_dst + 128) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-            }
-            fence_async_proxy();
-            tc_fence_before();
-            __syncthreads();
+            for (int h = 0; h < NH; ++h) l_acc[h] += pr[h];
 
             // ---- 5: O^T += V^T [P hi | P lo] ----
             if (tid == 0) {
