@@ -998,9 +998,13 @@ __device__ __forceinline__ Table<BITS> build_value_table(const float* cb, float 
 }
 
 // NH = query heads computed per item: 4 when the GQA group has at most 4 heads, else 8.
-template <typename T, int KB, int VB, bool TMA, int NH>
+// MODE = how the index rows reach the CTA: 0 direct global loads by every thread, 1 TMA boxes for K and
+// V rows, 2 TMA boxes for the K rows and 4-byte cp.async for V rows that are not 16-byte aligned.
+template <typename T, int KB, int VB, int MODE, int NH>
 __global__ void __launch_bounds__(kUThreads, kUCtasPerSm)
 decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_idx) {
+    constexpr bool TMA = MODE != 0;
+    constexpr bool v_by_tma = MODE == 1;
     extern __shared__ uint8_t smem_raw[];
     // aligned by hand: the swizzled TMA rows want 512-byte alignment
     UmmaSmem& sm = *reinterpret_cast<UmmaSmem*>(smem_raw + ((512u - (smem_u32(smem_raw) & 511u)) & 511u));
@@ -1128,16 +1132,39 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             if (lane == 0) {
                 const uint32_t bar = smem_u32(&sm.bar_in[warp]);
                 if (on0) {
-                    mbar_expect_tx(bar, on1 ? 4096u : 2048u);
+                    const uint32_t group_bytes = v_by_tma ? 2048u : 1024u;
+                    mbar_expect_tx(bar, on1 ? 2 * group_bytes : group_bytes);
                     tma_load_2d(smem_u32(sm.stage[warp][0]), &map_idx, kvh * kHalfDim, s0, bar);
-                    tma_load_2d(smem_u32(sm.stage[warp][1]), &map_idx, lay.v_idx + kvh * kHalfDim, s0, bar);
+                    if (v_by_tma) tma_load_2d(smem_u32(sm.stage[warp][1]), &map_idx, lay.v_idx + kvh * kHalfDim, s0, bar);
                     if (on1) {
                         tma_load_2d(smem_u32(sm.stage[warp][0]) + 1024u, &map_idx, kvh * kHalfDim, s1, bar);
-                        tma_load_2d(smem_u32(sm.stage[warp][1]) + 1024u, &map_idx, lay.v_idx + kvh * kHalfDim, s1, bar);
+                        if (v_by_tma)
+                            tma_load_2d(smem_u32(sm.stage[warp][1]) + 1024u, &map_idx, lay.v_idx + kvh * kHalfDim, s1, bar);
                     }
                 } else {
                     mbar_arrive(&sm.bar_in[warp]);
                 }
+            }
+            if constexpr (!v_by_tma) {
+                // V rows that do not start on 16-byte boundaries (1 or 2 KV heads on this GPU): the warp
+                // copies them with 4-byte cp.async, two rows per instruction, into the same swizzled order
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int row = 2 * i + (lane >> 4), word = lane & 15;
+                    if (tile * kUTile + 32 * warp + row < seq_len) {
+                        const int slot = (i < 8 ? s0 : s1) + (row & 15);
+                        cp_async4(sm.stage[warp][1] + row * kHalfDim + (((word >> 2) ^ ((row >> 1) & 3)) << 4) + ((word & 3) << 2),
+                                  p.cache + static_cast<int64_t>(slot) * p.total_bytes + lay.v_idx + kvh * kHalfDim + 4 * word);
+                    }
+                }
+                cp_async_commit();
+            }
+        };
+        // the staged V rows are complete (the K rows are covered by the barrier)
+        [[maybe_unused]] auto v_rows_landed = [&]() {
+            if constexpr (!v_by_tma) {
+                cp_async_wait<0>();
+                __syncwarp();
             }
         };
         [[maybe_unused]] auto fetch_staged = [&](int which, uint32_t (&w)[16], float& norm) {
@@ -1159,6 +1186,7 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 pf_blk = load_blk(t_begin + 1);
                 failed_in |= !mbar_wait(&sm.bar_in[warp], ph_in);
                 ph_in ^= 1u;
+                v_rows_landed();
                 fetch_staged(0, kw, nk);
                 fetch_staged(1, vw, nv);
                 __syncwarp();
@@ -1294,6 +1322,7 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 }
             }
             if constexpr (TMA) {
+                v_rows_landed();
                 if (tile + 1 < t_end) fetch_staged(1, vw, nv);
                 __syncwarp();                            // the staging rows are free again
                 if (tile + 2 < t_end) issue_tile(tile + 2, pf_blk);
@@ -1614,12 +1643,14 @@ static bool encode_cache_map(CUtensorMap* map, const uint8_t* cache, int64_t num
 // The TMA path needs 16-byte aligned box origins (KV heads a multiple of 4), tiles that never
 // straddle a block (power-of-two block size >= 16) and slot numbers that fit an int32 coordinate.
 // RQ_DECODE_NO_TMA=1 in the environment selects the cp.async path everywhere (for comparisons).
-static bool tma_eligible(const DecodeParams& p) {
+// The tensor-memory kernel only needs that for its K rows (always aligned); V rows of 1 or 2 KV heads
+// go through cp.async there.
+static bool tma_eligible(const DecodeParams& p, bool aligned_v_rows_needed) {
     static const bool disabled = [] {
         const char* e = std::getenv("RQ_DECODE_NO_TMA");
         return e != nullptr && e[0] != '\0' && e[0] != '0';
     }();
-    return !disabled && p.H % 4 == 0 && p.bs_shift >= 4 && aligned(p.cache, 16) &&
+    return !disabled && (p.H % 4 == 0 || !aligned_v_rows_needed) && p.bs_shift >= 4 && aligned(p.cache, 16) &&
            p.num_blocks * p.block_size <= INT32_MAX && p.total_bytes == p.H * 256;
 }
 
@@ -1641,7 +1672,7 @@ static int launch_decode(const DecodeParams& p, int num_seqs, cudaStream_t st) {
                                            const_cast<int2*>(p.seq_groups));
     if (int e = check_cuda(cudaGetLastError(), "rq_decode plan launch")) return e;
     alignas(64) CUtensorMap map_idx{}, map_norm{};
-    bool tma = tma_eligible(p);
+    bool tma = tma_eligible(p, !umma);
     const int64_t num_slots = p.num_blocks * p.block_size;
     if (tma) tma = encode_cache_map(&map_idx, p.cache, num_slots, p.total_bytes, kHalfDim, CU_TENSOR_MAP_SWIZZLE_64B);
     if (umma) {
@@ -1653,9 +1684,12 @@ static int launch_decode(const DecodeParams& p, int num_seqs, cudaStream_t st) {
             return RQ_OK;
         };
         const bool few = p.G <= 4;                                               // at most 4 query heads per item
-        if (int e = tma ? (few ? launch(decode_umma_kernel<T, KB, VB, true, 4>) : launch(decode_umma_kernel<T, KB, VB, true, 8>))
-                        : (few ? launch(decode_umma_kernel<T, KB, VB, false, 4>) : launch(decode_umma_kernel<T, KB, VB, false, 8>)))
-            return e;
+        const int mode = !tma ? 0 : (p.H % 4 == 0 ? 1 : 2);
+        int e = RQ_OK;
+        if (mode == 0) e = few ? launch(decode_umma_kernel<T, KB, VB, 0, 4>) : launch(decode_umma_kernel<T, KB, VB, 0, 8>);
+        else if (mode == 1) e = few ? launch(decode_umma_kernel<T, KB, VB, 1, 4>) : launch(decode_umma_kernel<T, KB, VB, 1, 8>);
+        else e = few ? launch(decode_umma_kernel<T, KB, VB, 2, 4>) : launch(decode_umma_kernel<T, KB, VB, 2, 8>);
+        if (e) return e;
         if (int e = check_cuda(cudaGetLastError(), "rq_decode tensor-memory launch")) return e;
     } else {
         if (tma) tma = encode_cache_map(&map_norm, p.cache, num_slots, p.total_bytes, kNormBox, CU_TENSOR_MAP_SWIZZLE_NONE);
