@@ -1180,18 +1180,11 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                     p.cache + static_cast<int64_t>(staged_slot) * p.total_bytes + (which ? lay.v_norm : lay.k_norm) + 4 * kvh));
             }
         };
+        // the first tile's rows are requested before the query set-up, which hides most of their latency
         if (!dead) {
             if constexpr (TMA) {
                 issue_tile(t_begin, load_blk(t_begin));
                 pf_blk = load_blk(t_begin + 1);
-                failed_in |= !mbar_wait(&sm.bar_in[warp], ph_in);
-                ph_in ^= 1u;
-                v_rows_landed();
-                fetch_staged(0, kw, nk);
-                fetch_staged(1, vw, nv);
-                __syncwarp();
-                if (t_begin + 1 < t_end) issue_tile(t_begin + 1, pf_blk);
-                pf_blk = load_blk(t_begin + 2);
             } else {
                 const uint8_t* first = slot_of(t_begin);
                 fetch_direct(0, first, kw, nk);
@@ -1238,6 +1231,19 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         }
         fence_async_proxy();
         __syncthreads();
+
+        if constexpr (TMA) {
+            if (!dead) {
+                failed_in |= !mbar_wait(&sm.bar_in[warp], ph_in);
+                ph_in ^= 1u;
+                v_rows_landed();
+                fetch_staged(0, kw, nk);
+                fetch_staged(1, vw, nv);
+                __syncwarp();
+                if (t_begin + 1 < t_end) issue_tile(t_begin + 1, pf_blk);
+                pf_blk = load_blk(t_begin + 2);
+            }
+        }
 
         float m_ref[NH], l_acc[NH];
 #pragma unroll
