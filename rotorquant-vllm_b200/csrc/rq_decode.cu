@@ -71,9 +71,17 @@ struct DecodeParams {
     const int2* seq_groups;               // [num_seqs] first and last group overlapping the sequence
     int num_seqs;
     int stream_warps;                     // warps of the streaming grid (multiple of 8)
-    int stream_groups;                    // groups of J warps; each owns one piece of the tile space
+    int stream_groups;                    // groups of J workers; each owns one piece of the tile space
+    const int32_t* group_cum;             // [groups + 1] running sum of the groups' weights (piece boundaries)
+    int weight_layers;                    // CTAs per weight layer (SM count) when the pieces are weighted, else 0
     int bs_shift;                         // log2(block_size) when it is a power of two, else -1
 };
+
+// The line of all tiles is cut into one piece per group, in proportion to the groups' weights:
+// piece g = [piece_begin(g), piece_begin(g + 1)).
+__device__ __forceinline__ int64_t piece_begin(const int32_t* __restrict__ cum, int groups, int64_t g, int64_t total) {
+    return total * __ldg(cum + g) / __ldg(cum + groups);
+}
 
 // ---- small PTX wrappers ------------------------------------------------------
 
@@ -552,13 +560,34 @@ __device__ __forceinline__ void stream_tile(uint32_t (*tbl_k)[8], uint32_t (*tbl
 }
 
 // Tiles of every sequence as an exclusive prefix sum: prefix[s] = sum_{s' < s} ceil(len[s'] / tile_tokens).
-// Then, for the merge, the first and last group whose piece overlaps each sequence (group g owns the
-// tiles [g * total / groups, (g + 1) * total / groups) of the line of all tiles).
+// First the piece boundaries of the groups (see piece_begin), then the prefix sums, then, for the merge,
+// the first and last group whose piece overlaps each sequence.
 __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num_seqs, int tile_tokens,
-                                   int32_t* __restrict__ prefix, int groups, int2* __restrict__ seq_groups) {
+                                   int32_t* __restrict__ prefix, int groups, int2* __restrict__ seq_groups,
+                                   int32_t* __restrict__ group_cum, int workers_per_group, int weight_layers) {
     __shared__ int warp_sums[32];
     __shared__ int carry;
     if (threadIdx.x == 0) carry = 0;
+    // Weights of the groups.  On one SM the CTAs that were launched first (lower block index) get
+    // the larger share of the issue slots while four of them run side by side, so that equal pieces
+    // would finish up to 40 % apart; worker c belongs to layer c / weight_layers and gets a piece
+    // in proportion to the speed measured for that layer.  weight_layers == 0: equal pieces.
+    for (int g = threadIdx.x; g <= groups; g += blockDim.x) {
+        int64_t acc = 0;                                        // sum of the weights of the workers before group g
+        const int64_t before = static_cast<int64_t>(g) * workers_per_group;
+        if (weight_layers > 0) {
+            const int w[4] = {1290, 1090, 950, 766};
+            int64_t left = before;
+            for (int layer = 0; left > 0; ++layer) {
+                const int64_t n = left < weight_layers ? left : weight_layers;
+                acc += n * w[layer < 3 ? layer : 3];
+                left -= n;
+            }
+        } else {
+            acc = before * 1024;
+        }
+        group_cum[g] = static_cast<int32_t>(acc);
+    }
     __syncthreads();
     for (int base = 0; base < num_seqs; base += blockDim.x) {
         const int s = base + threadIdx.x;
@@ -580,14 +609,24 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num
     }
     if (threadIdx.x == 0) prefix[num_seqs] = carry;
     __syncthreads();
-    const int64_t total = carry, ng = groups;
+    const int64_t total = carry;
+    // group holding tile t: the first g whose piece ends beyond t
+    auto group_of = [&](int64_t t) -> int {
+        int lo = 0, hi = groups - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (total * group_cum[mid + 1] / group_cum[groups] > t) hi = mid;
+            else lo = mid + 1;
+        }
+        return lo;
+    };
     for (int s = threadIdx.x; s < num_seqs; s += blockDim.x) {
         const int64_t a = prefix[s];
         const int64_t n = (max(__ldg(seq_lens + s), 0) + tile_tokens - 1) / tile_tokens;
         int2 r = make_int2(0, -1);                                      // empty sequence: no groups
         if (n > 0) {
-            r.x = static_cast<int>(((a + 1) * ng - 1) / total);        // group holding tile a
-            r.y = static_cast<int>(((a + n) * ng - 1) / total);        // group holding the last tile
+            r.x = group_of(a);
+            r.y = group_of(a + n - 1);
         }
         seq_groups[s] = r;
     }
@@ -613,8 +652,8 @@ decode_stream_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap m
     const int64_t group = wq / J;
     const int item = static_cast<int>(wq % J);
     if (group >= p.stream_groups) return;
-    int64_t x = group * total / p.stream_groups;
-    const int64_t x_end = (group + 1) * total / p.stream_groups;
+    int64_t x = piece_begin(p.group_cum, p.stream_groups, group, total);
+    const int64_t x_end = piece_begin(p.group_cum, p.stream_groups, group + 1, total);
     if (x >= x_end) return;
 
     // this lane's half of the codebooks (the half-table it builds for every token)
@@ -1017,8 +1056,8 @@ decode_umma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     const int64_t group = blockIdx.x / J;
     const int item = static_cast<int>(blockIdx.x % J);
     if (group >= p.stream_groups) return;
-    int64_t x = group * total / p.stream_groups;
-    const int64_t x_end = (group + 1) * total / p.stream_groups;
+    int64_t x = piece_begin(p.group_cum, p.stream_groups, group, total);
+    const int64_t x_end = piece_begin(p.group_cum, p.stream_groups, group + 1, total);
     if (x >= x_end) return;
 
     if (tid == 0) {
@@ -1491,7 +1530,6 @@ decode_stream_merge_kernel(const DecodeParams p) {
     const int item = kvh * p.head_groups + hl / kHeadsPerCta, h = hl % kHeadsPerCta;
     const int2 gr = __ldg(p.seq_groups + seq);
     const int64_t total = __ldg(p.tile_prefix + p.num_seqs);
-    const int64_t ng = p.stream_groups;
     const bool n_s = gr.y >= gr.x;                                     // the sequence has tiles
     float acc = 0.0f;
     float l_all = 0.0f;
@@ -1501,7 +1539,8 @@ decode_stream_merge_kernel(const DecodeParams p) {
         for (int64_t g0 = g_first; g0 <= g_last; g0 += 32) {           // normally one round
             const int64_t gi = g0 + lane;
             // groups whose piece is empty (only when there are more groups than tiles) wrote nothing
-            const bool live = gi <= g_last && (total >= ng || gi * total / ng < (gi + 1) * total / ng);
+            const bool live = gi <= g_last && piece_begin(p.group_cum, p.stream_groups, gi, total) <
+                                                  piece_begin(p.group_cum, p.stream_groups, gi + 1, total);
             const int64_t r = ((gi + seq) * J + item) * kHeadsPerCta + h;
             if (d < 32) {
                 const float m = live ? p.ws_m[r] : -INFINITY;
@@ -1571,7 +1610,9 @@ static void finish_plan(StreamPlan& pl, long long groups, long long J, int num_s
     pl.warps = static_cast<int>((groups * J + kDecodeWarps - 1) / kDecodeWarps * kDecodeWarps);
     pl.rows = static_cast<size_t>((groups + num_seqs) * J);
     // tile prefix sums [num_seqs + 1] (int32, padded to 8 bytes), then the group range of every sequence (int2)
-    pl.prefix_bytes = ((static_cast<size_t>(num_seqs + 2) / 2 * 2) * sizeof(int32_t) + static_cast<size_t>(num_seqs) * sizeof(int2) + 255) / 256 * 256;
+    // then the running weights of the groups (int32 [groups + 1])
+    pl.prefix_bytes = ((static_cast<size_t>(num_seqs + 2) / 2 * 2) * sizeof(int32_t) + static_cast<size_t>(num_seqs) * sizeof(int2) +
+                       static_cast<size_t>(groups + 1) * sizeof(int32_t) + 255) / 256 * 256;
     pl.bytes = pl.prefix_bytes + pl.rows * kHeadsPerCta * (kHeadDim + 2) * sizeof(float);
 }
 // Streaming kernel: groups get at least 8 tiles of 16 tokens each when the bound on the work
@@ -1675,7 +1716,8 @@ static int launch_decode(const DecodeParams& p, int num_seqs, cudaStream_t st) {
     const bool umma = decode_path() == DecodePath::kUmma;
     decode_plan_kernel<<<1, 1024, 0, st>>>(p.seq_lens, num_seqs, umma ? kUTile : kTile,
                                            const_cast<int32_t*>(p.tile_prefix), p.stream_groups,
-                                           const_cast<int2*>(p.seq_groups));
+                                           const_cast<int2*>(p.seq_groups), const_cast<int32_t*>(p.group_cum),
+                                           p.H * p.head_groups, p.weight_layers);
     if (int e = check_cuda(cudaGetLastError(), "rq_decode plan launch")) return e;
     alignas(64) CUtensorMap map_idx{}, map_norm{};
     bool tma = tma_eligible(p, !umma);
@@ -1782,11 +1824,15 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
     p.H = num_kv_heads; p.Hq = num_q_heads; p.G = G; p.head_groups = head_groups;
     p.tile_prefix = static_cast<const int32_t*>(workspace);
     p.seq_groups = reinterpret_cast<const int2*>(static_cast<const int32_t*>(workspace) + (num_seqs + 2) / 2 * 2);
+    p.group_cum = reinterpret_cast<const int32_t*>(p.seq_groups + num_seqs);
     const size_t rows = pl.rows * kHeadsPerCta;
     p.ws_o = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.prefix_bytes);
     p.ws_m = p.ws_o + rows * kHeadDim;
     p.ws_l = p.ws_m + rows;
     p.num_seqs = num_seqs; p.stream_warps = pl.warps; p.stream_groups = pl.groups;
+    // weighted pieces only for the tensor-memory kernel with (nearly) four CTAs on every SM
+    p.weight_layers = (decode_path() == DecodePath::kUmma && std::getenv("RQ_DECODE_EQUAL_PIECES") == nullptr &&
+                       1LL * pl.groups * num_kv_heads * head_groups > 3LL * 148) ? 148 : 0;
     p.bs_shift = -1;
     for (int sft = 0; sft < 31; ++sft)
         if ((1 << sft) == block_size) p.bs_shift = sft;
