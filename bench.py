@@ -44,7 +44,7 @@ UNIT = "tokens/s"
 # DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of
 # decode_split_kernel) divided by the algorithmic bytes of the same launch; see
 # profiles/decode_split_kernel_llama8b.md.  Used to scale `roofline.traffic` to this run's launch.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 156.5e6 / 143.2e6
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 155.8e6 / 143.2e6
 
 
 def parse_args():
