@@ -92,6 +92,20 @@ int rq_decompress(const uint8_t* packed, const float* norms, int64_t num_rows, i
                   void* stream);
 
 /*
+ * Paged decompress: K and V of whole cache blocks, read straight from the slot layout.  Replaces the
+ * gather + per-head slicing + two decompress launches of RQAttentionImpl._decompress_cache_paged
+ * (vllm/rq_backend.py:737-852, the part after torch.unique) and of _decompress_cache (:663-735).
+ *
+ *   blocks        int32[num_listed] physical block numbers (device), or NULL for blocks 0..num_listed-1
+ *   out_k, out_v  (num_listed, block_size, H, 128) in out_dtype: centroid[idx] * norm rounded once,
+ *                 rotated space; 16-byte aligned
+ */
+int rq_decompress_blocks(const uint8_t* kv_cache, int64_t num_blocks, int block_size, int total_bytes,
+                         int num_kv_heads, int head_dim, const int32_t* blocks, int64_t num_listed,
+                         const float* centroids_k, int n_centroids_k, const float* centroids_v,
+                         int n_centroids_v, void* out_k, void* out_v, int out_dtype, void* stream);
+
+/*
  * Scratch bytes rq_decode needs for `num_splits` context splits (0 = let the library choose
  * from max_seq_len; the same choice rq_decode makes).
  */
@@ -200,6 +214,24 @@ int rq_prefill_int8_staged(const void* q, void* out, int dtype, int64_t q_stride
                            const float* centroids_v, int n_centroids_v, const float* rotation,
                            float sm_scale, int* error_flag, int max_seq_len, void* workspace,
                            size_t workspace_bytes, void* stream);
+
+/*
+ * Measurement helper (no counterpart in the reference): enqueue one launch that keeps the tcgen05
+ * tensor pipe of every SM busy with back-to-back 128 x 256 MMAs from shared-memory operands --
+ * kind 0: int8 (kind::i8), kind 1: bf16 (kind::f16) -- `iters` rounds of four K steps each.
+ * *ops_out (host, optional) receives the operations (2 per multiply-add) of the launch; time the
+ * launch with events on `stream` to get the achievable tensor rate the prefill roofline uses.
+ * status_dev (device int, optional) is set to 1 if the kernel's bounded wait expired.
+ */
+int rq_probe_mma_peak(int kind, int iters, double* ops_out, int* status_dev, void* stream);
+
+/*
+ * Self test (no counterpart in the reference): one device thread waits, with the library's bounded
+ * mbarrier wait and a limit of `limit_cycles` SM clocks, on a barrier that nobody arrives on.
+ * status_dev[0] becomes 1 when the wait gave up as it must (0 if it reported completion),
+ * status_dev[1] the clocks it took / 1024.  The context stays usable.
+ */
+int rq_selftest_bounded_wait(long long limit_cycles, int* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

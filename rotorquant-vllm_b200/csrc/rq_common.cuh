@@ -126,7 +126,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Wait until the phase with the given parity has completed.  Every wait in this library is
 // bounded (about one second of SM clocks); false means the bound expired.
 constexpr long long kWaitCycles = 2000000000LL;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, long long limit_cycles) {
     const uint32_t addr = smem_u32(bar);
     long long start = 0;
     for (int spin = 0;; ++spin) {
@@ -138,8 +138,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
         if (spin == 0) start = clock64();
-        else if (clock64() - start > kWaitCycles) return false;
+        else if (clock64() - start > limit_cycles) return false;
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    return mbar_wait_for(bar, parity, kWaitCycles);
 }
 
 }  // namespace rq

@@ -332,6 +332,61 @@ __global__ void decompress_rows_kernel(const uint8_t* __restrict__ packed,
     }
 }
 
+// Paged decompress: the K and V rows of whole cache blocks, picked by a list of physical block
+// numbers, straight out of the slot layout.  Four threads per (token, head, K|V) row; thread q expands
+// index bytes 16q..16q+15.  Output row of (listed block j, position t, head h): (j * block_size + t) * H + h.
+template <typename T>
+__global__ void decompress_blocks_kernel(const uint8_t* __restrict__ cache, int total_bytes, int block_size, int H,
+                                         const int32_t* __restrict__ blocks, int64_t num_listed, int64_t num_blocks,
+                                         const float* __restrict__ cent_k, int n_k, const float* __restrict__ cent_v,
+                                         int n_v, T* __restrict__ out_k, T* __restrict__ out_v) {
+    __shared__ float cb[2][16];
+    if (threadIdx.x < 32) {
+        const int kv = threadIdx.x >> 4, i = threadIdx.x & 15;
+        cb[kv][i] = i < (kv ? n_v : n_k) ? (kv ? cent_v : cent_k)[i] : 0.f;
+    }
+    __syncthreads();
+    const int64_t rows_per_kind = num_listed * block_size * H;
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t r2 = i >> 2;
+    const int q = static_cast<int>(i & 3);
+    if (r2 >= 2 * rows_per_kind) return;
+    const int kind = r2 >= rows_per_kind ? 1 : 0;
+    const int64_t r = r2 - kind * rows_per_kind;
+    const int h = static_cast<int>(r % H);
+    const int64_t tok = r / H;
+    const int64_t j = tok / block_size;
+    const int pos = static_cast<int>(tok % block_size);
+    int64_t blk = blocks != nullptr ? static_cast<int64_t>(__ldg(blocks + j)) : j;
+    blk = blk < 0 ? 0 : (blk >= num_blocks ? num_blocks - 1 : blk);
+    const SlotLayout lay = slot_layout(H);
+    const uint8_t* slot = cache + (blk * block_size + pos) * total_bytes;
+    const uint8_t* src = slot + (kind ? lay.v_idx : lay.k_idx) + h * kHalfDim + 16 * q;   // 4-byte aligned at least
+    const uint32_t w[4] = {__ldg(reinterpret_cast<const uint32_t*>(src)), __ldg(reinterpret_cast<const uint32_t*>(src) + 1),
+                           __ldg(reinterpret_cast<const uint32_t*>(src) + 2), __ldg(reinterpret_cast<const uint32_t*>(src) + 3)};
+    const float norm = __ldg(reinterpret_cast<const float*>(slot + (kind ? lay.v_norm : lay.k_norm)) + h);
+    const float* c = cb[kind];
+    T* dst = (kind ? out_v : out_k) + r * kHeadDim + 32 * q;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float f[8];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const uint32_t byte = (w[k] >> (8 * b)) & 0xFFu;
+            f[2 * b] = __fmul_rn(c[byte >> 4], norm);
+            f[2 * b + 1] = __fmul_rn(c[byte & 15u], norm);
+        }
+        if constexpr (sizeof(T) == 4) {
+            reinterpret_cast<float4*>(dst + 8 * k)[0] = make_float4(f[0], f[1], f[2], f[3]);
+            reinterpret_cast<float4*>(dst + 8 * k)[1] = make_float4(f[4], f[5], f[6], f[7]);
+        } else {
+            *reinterpret_cast<uint4*>(dst + 8 * k) =
+                make_uint4(pack2<T>(f[0], f[1]), pack2<T>(f[2], f[3]), pack2<T>(f[4], f[5]),
+                           pack2<T>(f[6], f[7]));
+        }
+    }
+}
+
 // ---- host side -------------------------------------------------------------
 
 static int check_bounds_count(int n, const char* what) {
@@ -472,4 +527,52 @@ extern "C" int rq_decompress(const uint8_t* packed, const float* norms, int64_t 
             break;
     }
     return check_cuda(cudaGetLastError(), "rq_decompress launch");
+}
+
+extern "C" int rq_decompress_blocks(const uint8_t* kv_cache, int64_t num_blocks, int block_size, int total_bytes,
+                                    int num_kv_heads, int head_dim, const int32_t* blocks, int64_t num_listed,
+                                    const float* centroids_k, int n_centroids_k, const float* centroids_v,
+                                    int n_centroids_v, void* out_k, void* out_v, int out_dtype, void* stream) {
+    if (num_blocks < 0 || block_size <= 0 || num_kv_heads <= 0 || num_listed < 0)
+        return fail(RQ_ERR_INVALID_ARG, "rq_decompress_blocks: negative or zero size");
+    if (head_dim != kHeadDim)
+        return fail(RQ_ERR_UNSUPPORTED, "rq_decompress_blocks: head_dim %d (only 128)", head_dim);
+    if (total_bytes != num_kv_heads * kSlotPerHead)
+        return fail(RQ_ERR_INVALID_ARG, "rq_decompress_blocks: total_bytes %d != %d heads * 256", total_bytes,
+                    num_kv_heads);
+    if ((n_centroids_k != 8 && n_centroids_k != 16) || (n_centroids_v != 8 && n_centroids_v != 16))
+        return fail(RQ_ERR_UNSUPPORTED, "rq_decompress_blocks: codebooks must have 8 or 16 centroids");
+    if (out_dtype < RQ_DTYPE_F32 || out_dtype > RQ_DTYPE_BF16)
+        return fail(RQ_ERR_INVALID_ARG, "rq_decompress_blocks: unknown dtype %d", out_dtype);
+    if (num_listed == 0) return RQ_OK;
+    if (num_blocks == 0) return fail(RQ_ERR_INVALID_ARG, "rq_decompress_blocks: blocks listed but the cache is empty");
+    if (!kv_cache || !centroids_k || !centroids_v || !out_k || !out_v)
+        return fail(RQ_ERR_INVALID_ARG, "rq_decompress_blocks: null pointer");
+    if (!aligned(kv_cache, 16) || !aligned(out_k, 16) || !aligned(out_v, 16))
+        return fail(RQ_ERR_ALIGNMENT, "rq_decompress_blocks: kv_cache and outputs must be 16-byte aligned");
+    const int threads = 256;
+    const int64_t work = 2 * num_listed * block_size * num_kv_heads * 4;
+    if ((work + threads - 1) / threads > 0x7fffffffLL)
+        return fail(RQ_ERR_UNSUPPORTED, "rq_decompress_blocks: too many rows for one launch");
+    const unsigned grid = static_cast<unsigned>((work + threads - 1) / threads);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (out_dtype) {
+        case RQ_DTYPE_F32:
+            decompress_blocks_kernel<float><<<grid, threads, 0, st>>>(
+                kv_cache, total_bytes, block_size, num_kv_heads, blocks, num_listed, num_blocks, centroids_k,
+                n_centroids_k, centroids_v, n_centroids_v, static_cast<float*>(out_k), static_cast<float*>(out_v));
+            break;
+        case RQ_DTYPE_F16:
+            decompress_blocks_kernel<__half><<<grid, threads, 0, st>>>(
+                kv_cache, total_bytes, block_size, num_kv_heads, blocks, num_listed, num_blocks, centroids_k,
+                n_centroids_k, centroids_v, n_centroids_v, static_cast<__half*>(out_k), static_cast<__half*>(out_v));
+            break;
+        default:
+            decompress_blocks_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(
+                kv_cache, total_bytes, block_size, num_kv_heads, blocks, num_listed, num_blocks, centroids_k,
+                n_centroids_k, centroids_v, n_centroids_v, static_cast<__nv_bfloat16*>(out_k),
+                static_cast<__nv_bfloat16*>(out_v));
+            break;
+    }
+    return check_cuda(cudaGetLastError(), "rq_decompress_blocks launch");
 }

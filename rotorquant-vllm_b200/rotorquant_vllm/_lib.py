@@ -30,6 +30,7 @@ _SIGNATURES = {
                                _P, _I, _I, _P]),
     "rq_compress": (_I, [_P, _I, _L, _I, _L, _P, _P, _I, _P, _P, _P]),
     "rq_decompress": (_I, [_P, _P, _L, _I, _P, _I, _P, _I, _P]),
+    "rq_decompress_blocks": (_I, [_P, _L, _I, _I, _I, _I, _P, _L, _P, _I, _P, _I, _P, _P, _I, _P]),
     "rq_decode_workspace_bytes": (_Z, [_I, _I, _I, _I, _I, _I]),
     "rq_decode": (_I, [_P, _P, _I, _L, _L, _L, _L, _I, _I, _I, _I, _P, _L, _I, _I, _P, _L, _P, _P,
                        _I, _P, _I, _P, _F, _I, _P, _Z, _I, _P]),
@@ -37,6 +38,8 @@ _SIGNATURES = {
                                       _P, _I, _P, _I, _P, _F, _I, _I, _P]),
     "rq_prefill_int8": (_I, [_P, _P, _I, _L, _L, _L, _L, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P,
                              _L, _P, _P, _I, _P, _I, _P, _F, _P, _P]),
+    "rq_probe_mma_peak": (_I, [_I, _I, C.POINTER(C.c_double), _P, _P]),
+    "rq_selftest_bounded_wait": (_I, [C.c_longlong, _P, _P]),
     "rq_prefill_workspace_bytes": (_Z, [_I, _I, _I]),
     "rq_prefill_int8_staged": (_I, [_P, _P, _I, _L, _L, _L, _L, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P,
                                     _L, _P, _P, _I, _P, _I, _P, _F, _P, _I, _P, _Z, _P]),

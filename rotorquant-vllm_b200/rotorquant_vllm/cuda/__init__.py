@@ -3,7 +3,7 @@
 
 from .compress import compress_and_store, iso_compress, planar_compress
 from .decode import decode_workspace_bytes, fused_paged_rq_decode
-from .decompress import iso_decompress, planar_decompress
+from .decompress import decompress_blocks, decompress_cache_paged, iso_decompress, planar_decompress
 from .prefill import fused_paged_rq_int8_prefill
 from .rotation import validate_rotation
 
@@ -12,6 +12,8 @@ __all__ = [
     "planar_compress",
     "iso_decompress",
     "planar_decompress",
+    "decompress_blocks",
+    "decompress_cache_paged",
     "compress_and_store",
     "fused_paged_rq_decode",
     "fused_paged_rq_int8_prefill",

@@ -54,16 +54,44 @@ def slice_cache_heads(kv_cache: torch.Tensor, num_kv_heads: int, kv_lo: int, kv_
     return out
 
 
+class HeadGather:
+    """Buffers of the one collective of the head-sharded path, allocated once.
+
+    ``buffer`` is ``(world, num_seqs, H_Q/world, D)``; rank ``r`` lets its decode write straight into
+    ``local`` (= ``buffer[r]``, contiguous), then :meth:`gather` runs ONE in-place
+    ``all_gather_into_tensor`` on the current stream -- no list of tensors, no concatenation, no
+    allocation, so the call can sit inside a captured CUDA graph.  ``result`` is the gathered output
+    as a view ``(num_seqs, world, H_Q/world, D)``: the query-head axis split into (owner rank, head
+    on that rank), heads in their global order; ``result.reshape(num_seqs, H_Q, D)`` gives the dense
+    tensor where one is wanted (that copies).
+    """
+
+    def __init__(self, num_seqs: int, heads_per_rank: int, head_dim: int, dtype: torch.dtype, device,
+                 group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.buffer = torch.zeros(self.world, num_seqs, heads_per_rank, head_dim, dtype=dtype, device=device)
+        self.local = self.buffer[self.rank]
+        self.result = self.buffer.permute(1, 0, 2, 3)
+
+    def gather(self) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.buffer.view(-1, *self.local.shape[1:]), self.local, group=self.group)
+        return self.result
+
+
 def gather_head_outputs(local_out: torch.Tensor, group=None) -> torch.Tensor:
-    """All-gather rank-local head outputs ``(num_seqs, H_Q/n, D)`` into ``(num_seqs, H_Q, D)``.
+    """All-gather rank-local head outputs ``(num_seqs, H_Q/n, D)`` into a dense ``(num_seqs, H_Q, D)``.
 
     Ranks hold consecutive head ranges (see :func:`shard_heads`).  One collective, issued on the
-    current stream by the backend of ``group`` (NCCL over NVLink on GPUs, gloo on CPU).
+    current stream by the backend of ``group`` (NCCL over NVLink on GPUs, gloo on CPU).  Convenience
+    form that allocates its result; a serving loop keeps a :class:`HeadGather` instead.
     """
     world = dist.get_world_size(group)
     if world == 1:
         return local_out
     local_out = local_out.contiguous()
-    parts = [torch.empty_like(local_out) for _ in range(world)]
-    dist.all_gather(parts, local_out, group=group)
-    return torch.cat(parts, dim=1)
+    gathered = torch.empty(world, *local_out.shape, dtype=local_out.dtype, device=local_out.device)
+    dist.all_gather_into_tensor(gathered.view(-1, *local_out.shape[1:]), local_out, group=group)
+    return gathered.permute(1, 0, 2, 3).reshape(local_out.shape[0], world * local_out.shape[1], local_out.shape[2])

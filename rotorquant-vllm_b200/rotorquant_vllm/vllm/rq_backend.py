@@ -247,6 +247,11 @@ class RQAttentionImpl(FlashAttentionImpl):
         self._v_quantizer = self._k_quantizer if self._v_bits == self._k_bits else make(self._v_bits)
 
         rot = _build_rotation_matrix(self._k_quantizer, self.head_size, device)
+        # Structure check with its one host copy happens here, at build time; the launchers then
+        # recognise the matrix by identity and never synchronise on the request path.
+        from rotorquant_vllm.cuda.rotation import validate_rotation
+
+        validate_rotation(rot)
         self._rq_rot = rot
         self._rq_rot_T = rot.T.contiguous()
         self._rq_rot_T_even = self._rq_rot_T[:, 0::2].contiguous()
@@ -304,6 +309,35 @@ class RQAttentionImpl(FlashAttentionImpl):
         """
         _compress_and_store_fn(key, value, kv_cache, slot_mapping, self._rq_rot,
                                self._k_quantizer.boundaries, self._v_quantizer.boundaries)
+
+    # -- decompress (for callers that want plain K/V tensors; attention itself never decompresses) --
+
+    def _decompress_cache(self, kv_cache: torch.Tensor, compute_dtype: torch.dtype):
+        """The whole cache as ``(NB, BS, H, D)`` K and V in ``compute_dtype``, rotated space
+        (upstream :663-735), in one launch."""
+        from rotorquant_vllm.cuda.decompress import decompress_blocks
+
+        return decompress_blocks(kv_cache, None, self.num_kv_heads, self._k_quantizer.centroids,
+                                 self._v_quantizer.centroids, compute_dtype)
+
+    def _decompress_cache_paged(self, kv_cache: torch.Tensor, block_table: torch.Tensor,
+                                seq_lens: torch.Tensor, compute_dtype: torch.dtype, out_k=None, out_v=None):
+        """Only the physical blocks ``block_table`` references: ``(key_cache, value_cache,
+        remapped_block_table)`` as upstream (:737-852).  ``out_k`` / ``out_v`` ``(max_tokens, H, D)``
+        receive the rows when they are large enough, as upstream."""
+        from rotorquant_vllm.cuda.decompress import decompress_cache_paged
+
+        k, v, remapped = decompress_cache_paged(kv_cache, block_table, seq_lens, self.num_kv_heads,
+                                                self._k_quantizer.centroids, self._v_quantizer.centroids,
+                                                compute_dtype)
+        tokens = k.shape[0] * k.shape[1]
+        if out_k is not None and out_k.shape[0] >= tokens:
+            out_k[:tokens].copy_(k.reshape(tokens, *k.shape[2:]))
+            k = out_k[:tokens].reshape(k.shape)
+        if out_v is not None and out_v.shape[0] >= tokens:
+            out_v[:tokens].copy_(v.reshape(tokens, *v.shape[2:]))
+            v = out_v[:tokens].reshape(v.shape)
+        return k, v, remapped
 
     # -- forward -------------------------------------------------------------------------------
 

@@ -24,14 +24,4 @@ def params(tag: str, k_bits: int, v_bits: int) -> dict:
     }
 
 
-def attention_tolerance(ref_rot: torch.Tensor, ref_out: torch.Tensor, dtype: torch.dtype,
-                        floor: float = 2e-3) -> torch.Tensor:
-    """Element-wise bound on |out - reference|: 2e-3, or, where the reference output itself is
-    coarser than that, one unit in the last place of the largest rotated element of the 4-block
-    (a legal rounding flip of one rotated element moves the four outputs of its block by that
-    much) plus one unit in the last place of the output."""
-    scale = 1.0 if dtype == torch.bfloat16 else 8.0
-    blk = ref_rot.abs().reshape(*ref_rot.shape[:-1], 32, 4).amax(-1, keepdim=True)
-    blk = blk.expand(*ref_rot.shape[:-1], 32, 4).reshape(ref_rot.shape)
-    unit = (helpers.ulp_bf16(blk) + helpers.ulp_bf16(ref_out.float())) / scale
-    return torch.clamp(unit, min=floor)
+from oracle.tolerance import attention_tolerance  # noqa: E402,F401  (shared with smoke and bench)

@@ -74,7 +74,4 @@ def load_case(name: str) -> dict:
     return out
 
 
-def ulp_bf16(x: torch.Tensor) -> torch.Tensor:
-    """Size of one bf16 unit in the last place at |x| (fp32 tensor)."""
-    e = torch.floor(torch.log2(x.abs().float().clamp_min(1e-30)))
-    return torch.pow(2.0, e - 7)
+from oracle.tolerance import ulp_bf16  # noqa: E402,F401

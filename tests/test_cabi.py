@@ -60,6 +60,21 @@ def test_bad_arguments_are_rejected_without_a_device():
     assert st == _lib.RQ_ERR_WORKSPACE and b"workspace" in L.rq_last_error()
     with pytest.raises(ValueError):
         _lib.check(st)
+    # fewer query heads than KV heads: no size, and an argument error from both decode entry points
+    # (never a division by zero in the host-side planning)
+    assert L.rq_decode_workspace_bytes(4, 4, 8, 128, 2048, 0) == 0
+    assert L.rq_decode_workspace_bytes(4, 12, 8, 128, 2048, 0) == 0
+    st = L.rq_decode(16, 16, 2, 4096, 128, 4096, 128, 4, 4, 8, 128, 16, 8, 16, 2048, 16, 8, 16, 16, 8,
+                     16, 8, 16, 0.088, 128, 16, 1 << 20, 0, None)
+    assert st == _lib.RQ_ERR_INVALID_ARG
+    st = L.rq_decode_static_scratch(16, 16, 2, 4096, 128, 4096, 128, 4, 4, 8, 128, 16, 8, 16, 2048, 16, 8,
+                                    16, 16, 8, 16, 8, 16, 0.088, 128, 0, None)
+    assert st == _lib.RQ_ERR_INVALID_ARG and b"query heads" in L.rq_last_error()
+    # paged decompress: slot size must match the head count; the self tests check their arguments
+    st = L.rq_decompress_blocks(16, 4, 16, 1000, 8, 128, None, 2, 16, 8, 16, 8, 16, 16, 2, None)
+    assert st == _lib.RQ_ERR_INVALID_ARG
+    assert L.rq_selftest_bounded_wait(0, None, None) == _lib.RQ_ERR_INVALID_ARG
+    assert L.rq_probe_mma_peak(2, 16, None, None, None) == _lib.RQ_ERR_INVALID_ARG
     # zero work is fine
     assert L.rq_compress(None, 2, 0, 128, 128, None, None, 7, None, None, None) == 0
     # forced: one piece per sequence -> 4 groups of 8 warps; rows = (groups + sequences) * 8 items, 8 heads each

@@ -97,11 +97,19 @@ def test_decode_matches_oracle_on_fresh_cases(tag, kb, vb, H, HQ, lens, bs):
     _assert_close(out, _oracle(c), _oracle(c, rotated=True), torch.bfloat16, f"{tag} H={H}")
 
 
-@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_rotated_space_output_within_2e3(dtype):
-    """R = I with pre-rotated queries exposes round_T(o_rot): it must be within 2e-3 (plus half a
-    unit in the last place of the rounding itself) of the oracle's fp32 rotated output."""
-    c = _fresh_case("iso_fast", 3, 3, 8, 32, [4096, 512, 64, 2048], 16, dtype, seed=5)
+@pytest.mark.parametrize("tag,kb,vb,H,HQ,lens,dtype", [
+    ("iso_fast", 3, 3, 8, 32, [4096, 512, 64, 2048], torch.bfloat16),     # llama-8B grouping
+    ("iso_fast", 3, 3, 8, 32, [4096, 512, 64, 2048], torch.float16),
+    ("planar", 4, 3, 4, 28, [3000, 129, 700], torch.bfloat16),            # 4-bit K tables, G = 7
+    ("iso_full", 3, 3, 1, 8, [5000, 300], torch.bfloat16),                # one KV head per GPU, G = 8
+    ("iso_fast", 4, 4, 2, 32, [1500, 77], torch.bfloat16),                # 4-bit K and V, G = 16
+    ("iso_full", 3, 4, 4, 16, [900, 2048], torch.float16),                # 4-bit V tables, fp16
+])
+def test_rotated_space_output_within_2e3(tag, kb, vb, H, HQ, lens, dtype):
+    """R = I with pre-rotated queries exposes round_T(o_rot): it must be within 2e-4 (plus half a
+    unit in the last place of the rounding itself) of the oracle's fp32 rotated output -- ten times
+    tighter than the 2e-3 bar, in every table / grouping variant the kernel is instantiated for."""
+    c = _fresh_case(tag, kb, vb, H, HQ, lens, 16, dtype, seed=5)
     ref_rot = _oracle(c, rotated=True)
     q_rot = (c["q"].float() @ c["R"].T).to(dtype)
     c2 = dict(c)
@@ -111,6 +119,32 @@ def test_rotated_space_output_within_2e3(dtype):
     half_ulp = helpers.ulp_bf16(ref_rot) / (2.0 if dtype == torch.bfloat16 else 16.0)
     err = (got - ref_rot).abs() - half_ulp
     assert err.max().item() <= 2e-4, err.max().item()
+
+
+def test_scores_that_keep_growing_move_the_reference_maximum():
+    """Keys whose norms grow along the sequence make later tiles outgrow the softmax reference of
+    the first tile again and again: the rare path that hands a tile back, moves the maxima and
+    rescales the accumulated output."""
+    p = gpu_util.params("iso_fast", 3, 3)
+    H, HQ, bs, n = 8, 32, 16, 1500
+    seq_lens = torch.tensor([n, 700], dtype=torch.int32)
+    bt, nb = syn.make_block_table(seq_lens, bs, 3)
+    slots = syn.slot_mapping_for(bt, seq_lens, bs)
+    key, value = syn.make_kv(int(seq_lens.sum()), H, 128, torch.bfloat16, 3)
+    q = syn.make_queries(2, HQ, 128, torch.bfloat16, 3)
+    # every key points along its sequence's first query head, with a length that grows 30-fold
+    ramp = torch.cat([torch.linspace(0.2, 6.0, n), torch.linspace(6.0, 0.2, 700)])
+    q_rot = q.float() @ p["R"].T
+    direction = torch.cat([q_rot[0, 0].expand(n, 128), q_rot[1, 0].expand(700, 128)]) @ p["R"]
+    key = (key.float() * 0.3 + direction[:, None, :] * ramp[:, None, None]).to(torch.bfloat16)
+    cache = torch.zeros(nb, bs, H * 256, dtype=torch.uint8)
+    rq_oracle.compress_and_store(key, value, cache, slots, p["R"], p["k_boundaries"], p["v_boundaries"])
+    c = dict(p)
+    c.update(q=q, kv_cache=cache, block_table=bt, seq_lens=seq_lens, num_kv_heads=H,
+             sm_scale=1.0 / math.sqrt(128))
+    for splits in (0, 1):
+        out = _run_case(c, num_splits=splits)
+        _assert_close(out, _oracle(c), _oracle(c, rotated=True), torch.bfloat16, f"growing scores splits={splits}")
 
 
 def test_llama8b_shape_small_batch_and_output_buffer():
@@ -161,19 +195,32 @@ def test_bytes_past_the_end_of_a_sequence_are_ignored(dtype):
     _assert_close(out, _oracle(c), _oracle(c, rotated=True), dtype, "garbage tail")
 
 
-def test_streaming_kernels_in_a_subprocess():
-    """RQ_DECODE_PATH=stream selects the warp-streaming kernel (read once per process), with and
-    without its TMA ring: run the golden and edge cases under it in child processes."""
+def test_row_copy_staging_in_a_subprocess():
+    """RQ_DECODE_NO_TMA=1 (read once per process) stages the index rows with one bulk copy per
+    token instead of TMA boxes, the path every unusual block size takes: run the golden and edge
+    cases under it in a child process."""
     import os
     import subprocess
     import sys
 
-    if os.environ.get("RQ_DECODE_PATH") == "stream":
-        pytest.skip("already running under the streaming kernel")
+    if os.environ.get("RQ_DECODE_NO_TMA"):
+        pytest.skip("already running with row copies")
     here = os.path.dirname(os.path.abspath(__file__))
-    for extra in ({"RQ_DECODE_PATH": "stream"}, {"RQ_DECODE_PATH": "stream", "RQ_DECODE_NO_TMA": "1"}):
-        env = dict(os.environ, **extra)
-        res = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_decode_gpu.py"), "-x", "-q",
-                              "-m", "gpu", "-k", "golden or past_the_end or fresh or rotated_space"],
-                             env=env, capture_output=True, text=True, timeout=900)
-        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    env = dict(os.environ, RQ_DECODE_NO_TMA="1")
+    res = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_decode_gpu.py"), "-x", "-q",
+                          "-m", "gpu", "-k", "golden or past_the_end or fresh or growing"],
+                         env=env, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+def test_many_sequences_use_the_plan_launch():
+    """More sequences than an attention CTA scans by itself (256): the tile prefix sums come from
+    the separate plan launch.  300 short ragged sequences, a few of them empty."""
+    gen = torch.Generator().manual_seed(77)
+    lens = torch.randint(1, 200, (300,), generator=gen).tolist()
+    lens[5] = 0
+    lens[299] = 0
+    c = _fresh_case("iso_fast", 3, 3, 4, 16, lens, 16, torch.bfloat16, seed=8)
+    out = _run_case(c)
+    _assert_close(out, _oracle(c), _oracle(c, rotated=True), torch.bfloat16, "300 sequences")
+    assert torch.all(out[5] == 0) and torch.all(out[299] == 0)

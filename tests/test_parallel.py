@@ -52,6 +52,12 @@ def _rank_main(rank: int, world: int, port: int, result_path: str):
                                  c["seq_lens"], c["k_centroids"], c["v_centroids"], c["R"],
                                  kv_hi - kv_lo, 128, 16, sm_scale=c["sm_scale"])
         full = parallel.gather_head_outputs(local)
+        # the allocation-free form: the rank's heads are written into its slice, one in-place collective
+        hg = parallel.HeadGather(local.shape[0], local.shape[1], 128, local.dtype, "cpu")
+        hg.local.copy_(local)
+        again = hg.gather()
+        assert again.shape == (local.shape[0], world, local.shape[1], 128)
+        assert torch.equal(again.reshape(full.shape), full)
         if rank == 0:
             torch.save(full, result_path)
     finally:

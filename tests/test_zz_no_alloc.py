@@ -15,7 +15,7 @@ import torch
 
 import gpu_util
 from gpu_util import DEV
-from oracle import rq_oracle
+from oracle import rq_oracle, tolerance
 from rotorquant_vllm import _lib
 from rotorquant_vllm import synthetic as syn
 
@@ -66,6 +66,13 @@ def test_static_scratch_decode_matches_regular_decode_twice():
         diff = (got.float() - want.float()).abs().max().item()
         assert diff <= 2e-3, diff
         assert not bool(torch.isnan(got.float()).any())
+        # and against the oracle, so that a fault shared by both entry points cannot pass
+        p = gpu_util.params("iso_fast", 3, 3)
+        args = (c["q"].cpu(), c["cache"].cpu(), c["bt"].cpu(), c["sl"].cpu(), p["k_centroids"], p["v_centroids"],
+                p["R"], H, 128, bs)
+        worst, over = tolerance.excess(got.cpu(), rq_oracle.decode(*args, return_rotated_fp32=True),
+                                       rq_oracle.decode(*args), torch.bfloat16)
+        assert over == 0, (worst, over)
 
 
 def test_static_scratch_rejects_oversized_calls():
