@@ -148,7 +148,7 @@ int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq, int64_t
  * The function calls no cudaMalloc / cudaFree and no allocating library routine.
  *
  * Arguments and results are those of rq_decode without `workspace` / `workspace_bytes`.
- *   - A call whose splits need more than RQ_DECODE_STATIC_SCRATCH_BYTES (see
+ *   - A call whose partial results need more than RQ_DECODE_STATIC_SCRATCH_BYTES (16 MiB; see
  *     rq_decode_workspace_bytes) is rejected with RQ_ERR_WORKSPACE; nothing is launched.
  *   - The first call on each device looks up the device address of the area
  *     (cudaGetSymbolAddress, with that device current).  Make that first call before any stream
@@ -158,7 +158,7 @@ int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq, int64_t
  *     calls that overlap on the GPU (different streams) race on it: keep them on one stream or
  *     order them yourself.
  */
-#define RQ_DECODE_STATIC_SCRATCH_BYTES (4u << 20)
+#define RQ_DECODE_STATIC_SCRATCH_BYTES (16u << 20)
 int rq_decode_static_scratch(const void* q, void* out, int dtype, int64_t q_stride_seq,
                              int64_t q_stride_head, int64_t o_stride_seq, int64_t o_stride_head,
                              int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,

@@ -4,32 +4,42 @@
 // Triton kernel (one program per (sequence, query head), CUDA-core dot products, no split-KV)
 // and the two dense 128x128 rotations its launcher runs around it.
 //
-// Work decomposition.  The (sequence, 128-token tile) space of the batch is one line of tiles,
-// cut into contiguous pieces; a CTA streams the tiles of one piece for one (KV head, group of up
-// to 8 query heads) and leaves one partial result per sequence its piece touches.  A second
-// launch merges the partial results of every (sequence, query head), rounds, and applies R.  The
-// 136 payload bytes of a (token, KV head) are read from HBM exactly once for all query heads of
-// the GQA group.
+// Work decomposition.  A tile is 128 (token, KV head) pairs: T = 128 / Ht consecutive tokens of one
+// sequence times a "head tile" of Ht KV heads (Ht = all KV heads of this GPU when there are 1, 2, 4
+// or 8 of them).  With a whole head tile in one CTA the payload of a token -- K indices, K norms,
+// V indices, V norms of all its heads, 136 * H contiguous bytes of the slot -- arrives as ONE row of
+// ONE TMA box per block of tokens, norms included.  (One CTA per KV head, as the first versions had
+// it, needs a 64-byte K row, a 64-byte V row and two norm sectors per token and head: about 4.5
+// memory requests for 136 bytes.  The SM's TMA unit was measured at 0.17 such rows per cycle, 16-byte
+// cp.async copies at about 0.2, against 0.75 requests per cycle at the HBM roofline.)
+// The (sequence, tile) space of the batch is one line of tiles, cut into contiguous pieces; a CTA
+// streams the tiles of one piece for one (head tile, group of up to 8 query heads per KV head) and
+// leaves one partial result per sequence its piece touches.  A second launch merges the partial
+// results of every (sequence, query head), rounds, and applies R.
 //
-// The attention CTA is warp specialised: four compute warps (thread t owns token t of the tile
-// and TMEM lane t) and one issuer warp that owns every asynchronous engine -- it fills a ring of
-// index-row tiles with TMA boxes (or per-row bulk copies), and issues the tcgen05 MMAs when the
-// compute warps have published their operands.  Compute warps never issue a copy or an MMA and
-// meet no block-wide barrier inside the tile loop; everything is ordered by mbarriers.
+// The attention CTA is warp specialised: four compute warps (thread t owns pair t of the tile and
+// TMEM lane t) and one issuer warp that owns every asynchronous engine -- it fills a ring of staged
+// tiles with TMA boxes and issues the tcgen05 MMAs when the compute warps have published their
+// operands.  Compute warps never issue a copy or an MMA and meet no block-wide barrier inside the
+// tile loop; everything is ordered by mbarriers.
 //
 // Arithmetic (matches "reference decompress + SDPA"):
 //   q_rot   = round_T(q @ R^T)            exact FMA chain per 4x4 block, computed per part
-//   K, V    = round_T(centroid[idx]*norm) exactly the decompressed values: each token gets a
+//   K, V    = round_T(centroid[idx]*norm) exactly the decompressed values: each pair gets a
 //             table of its 8/16 rounded products, elements are fetched from it with PRMT
 //   scores  = int8 tensor-core mma over 15-bit integer images of q_rot and K (exact for K, 2^-14
-//             of the row maximum for q), fp32 scaling, exp2-domain softmax against a reference
-//             maximum per head (exact maximum of the part's first tile; it moves later only when
-//             a score exceeds it by 2^8)
+//             of the row maximum for q): S^T = K Q^T with the 128 pairs on the M side and the digit
+//             planes of ALL query heads of the head tile on the N side; a pair reads the columns of
+//             its own KV head.  fp32 scaling, exp2-domain softmax against a reference maximum per
+//             head (exact maximum of the part's first tile; it moves later only when a score
+//             exceeds it by 2^8)
 //   P @ V   = tensor-core mma with P split into hi + lo parts (two T-precision terms, ~16 bits),
-//             fp32 accumulate in tensor memory
+//             fp32 accumulate in tensor memory; the 16 pairs of one MMA k-step belong to one KV
+//             head, so each k-step accumulates into that head's output columns
 //   out     = round_T(round_T(o / l) @ R)  in the merge kernel
 #include <cuda.h>          // CUtensorMap (types only; the encoder is looked up at run time)
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -40,16 +50,20 @@
 
 namespace rq {
 
-constexpr int kHeadsPerCta = 8;              // query heads per item (mma N of P@V is 2 x 8)
-constexpr int kTileTokens = 128;             // tokens per tile = compute threads per CTA
+constexpr int kQPerHead = 8;                 // query-head slots per KV head of a partial row / of one item
+constexpr int kPairs = 128;                  // (token, KV head) pairs per tile = compute threads per CTA
 constexpr int kComputeThreads = 128;
 constexpr int kDecodeThreads = 160;          // + the issuer warp
 constexpr int kIssuerWarp = 4;
-constexpr uint32_t kTmemCols = 128;          // columns allocated per CTA
-constexpr uint32_t kColKhi = 0, kColKlo = 32, kColS = 64, kColO = 96;
+constexpr uint32_t kTmemCols = 256;          // columns allocated per CTA
+constexpr uint32_t kColKhi = 0, kColKlo = 32, kColS = 64, kColS2 = 128, kColO = 192;
+constexpr int kMaxCols = 64;                 // columns of one S accumulator and of O: head tile x 2 x query heads
 constexpr int kInlinePlanSeqs = 256;         // up to this many sequences the CTAs scan seq_lens themselves
 constexpr int kMaxLayers = 4;                // launch layers with their own piece weight
-constexpr int kMaxCtasPerSm = 3;
+constexpr int kCtasPerSm = 2;
+constexpr int kRingBytes = 54 * 1024;        // staged tiles (two or three stages)
+constexpr int kMaxStages = 3;
+constexpr int kRegions = 4;                  // K indices, K norms, V indices, V norms
 
 struct DecodeParams {
     const void* q;
@@ -67,8 +81,11 @@ struct DecodeParams {
     float qk_scale;                        // sm_scale * log2(e)
     int H, Hq, G;                          // KV heads, query heads, Hq / H
     int head_groups;                       // ceil(G / 8)
-    float* ws_o;                           // [row][8 heads][128], row = (group + sequence) * J + item
-    float* ws_m;                           // [row][8 heads]
+    int ht, ht_shift;                      // KV heads per tile (1, 2, 4 or 8)
+    int ttok, ttok_shift;                  // tokens per tile = 128 / ht
+    int n_cols;                            // columns of S and of O: max(16, ht * 2 * NH)
+    float* ws_o;                           // [row][ht * 8 slots][128], row = (group + sequence) * J + item
+    float* ws_m;                           // [row][ht * 8]
     float* ws_l;
     void* out;
     int64_t o_stride_seq, o_stride_head;
@@ -77,12 +94,30 @@ struct DecodeParams {
     int groups;                            // pieces; CTA = (group, item)
     int inline_plan;                       // the attention CTAs compute the prefix sums themselves
     int bs_shift;                          // log2(block_size) when it is a power of two, else -1
-    int box_tokens;                        // tokens per TMA box (16, or 8 for block size 8)
+    // staging: a stage holds, per region, an array [ttok][w] of the region's bytes of every token
+    int n_regions;                         // 1: the whole payload of the head tile is contiguous; else 4
+    int reg_w[kRegions];                   // bytes copied per token and region (multiple of 16)
+    int reg_base[kRegions];                // offset of the region's array inside a stage
+    int stage_bytes, stages;
+    int box_rows;                          // tokens per TMA box (0: no TMA, the issuer warp copies 4-byte words)
+    int v_aligned;                         // V rows sit on 16-byte boundaries of the stage
     int layer_ctas;                        // CTAs per launch layer (SM count) when pieces are weighted, else 0
     int num_layers;
     int layer_w[kMaxLayers];               // piece weight of the CTAs of each launch layer
     unsigned long long* trace;             // development builds only
 };
+
+// Development builds (-DRQ_DECODE_TRACE) record clock64() at the phase boundaries of a few CTAs.
+#ifdef RQ_DECODE_TRACE
+#define RQ_TRACE(point)                                                                             \
+    do {                                                                                            \
+        if (trace_row != nullptr && lane == 0 && it < 64) trace_row[it * 16 + (point)] = clock64(); \
+    } while (0)
+#else
+#define RQ_TRACE(point) \
+    do {                \
+    } while (0)
+#endif
 
 // ---- pieces -----------------------------------------------------------------------------------
 //
@@ -104,6 +139,21 @@ __host__ __device__ inline int64_t weight_cum(int64_t n, int layer_ctas, int num
 __device__ __forceinline__ int64_t piece_begin(const DecodeParams& p, int64_t g, int64_t total, int J) {
     return total * weight_cum(g * J, p.layer_ctas, p.num_layers, p.layer_w) /
            weight_cum(static_cast<int64_t>(p.groups) * J, p.layer_ctas, p.num_layers, p.layer_w);
+}
+
+// Byte ranges of the four payload regions of head tile `h0 .. h0 + ht` inside a slot of H heads:
+// start[r] (may be 4, 8 or 12 bytes past a 16-byte boundary) and the 16-byte boundary below it.
+struct RegionWindow {
+    int start[kRegions], x[kRegions];
+};
+__host__ __device__ inline RegionWindow region_window(int H, int h0) {
+    RegionWindow rw;
+    rw.start[0] = kHalfDim * h0;                       // K indices
+    rw.start[1] = kHalfDim * H + 4 * h0;               // K norms
+    rw.start[2] = (kHalfDim + 4) * H + kHalfDim * h0;  // V indices
+    rw.start[3] = (2 * kHalfDim + 4) * H + 4 * h0;     // V norms
+    for (int r = 0; r < kRegions; ++r) rw.x[r] = rw.start[r] & ~15;
+    return rw;
 }
 
 // ---- small PTX wrappers ------------------------------------------------------
@@ -164,13 +214,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
-// Untiled bulk copy of `bytes` (a multiple of 16; both addresses 16-byte aligned) global -> shared.
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar_addr) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-        "l"(src), "r"(bytes), "r"(bar_addr)
-        : "memory");
+// 4-byte asynchronous copy global -> shared; the mbarrier receives one arrival (already counted in
+// its expected arrivals) when every copy this thread has issued so far has landed.
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -287,34 +339,28 @@ __device__ __forceinline__ Table<BITS> build_value_table(const float* cb, float 
 }
 
 // ---- shared memory of the attention CTA ---------------------------------------------------------
-//
-// MODE = how the index rows of a tile reach the ring:
-//   1  TMA boxes of 16 (or 8) tokens x 64 B for K and for V rows, 64-byte swizzle (KV heads a multiple
-//      of 4, so V rows start on 16-byte boundaries; power-of-two block size >= 8)
-//   2  the same boxes for K; V rows, which start 4, 8 or 12 bytes past a 16-byte boundary, as boxes of
-//      80 B from the boundary below, unswizzled (power-of-two block size >= 8)
-//   0  one 64-byte (K) and one 80-byte (V) bulk copy per token, unswizzled: any block size
-template <int MODE>
 struct DecodeSmem {
-    static constexpr int kStages = MODE == 1 ? 2 : 3;
-    static constexpr int kVPitch = MODE == 1 ? 64 : 80;
-    static constexpr int kCtasPerSm = MODE == 1 ? 3 : 2;
-    alignas(1024) uint8_t ring_k[kStages][kTileTokens * kHalfDim];
-    alignas(128) uint8_t ring_v[kStages][kTileTokens * kVPitch];
-    alignas(128) uint16_t v[kTileTokens * kHeadDim];   // V tile: core (token/8)*16 + pos/8, core row token%8
-    uint16_t p[kTileTokens * 16];                      // P tile: core (token/8)*2 + n/8, core row token%8
-    uint8_t q[16 * kHeadDim];                          // Q digit planes, K-major: core (n/8)*8 + pos/16
+    alignas(128) uint16_t v[kPairs * kHeadDim];        // V tile: core (pair/8)*16 + pos/8, core row pair%8
+    uint16_t p[kPairs * 16];                           // P tile: core (pair/8)*2 + n/8, core row pair%8
+    uint8_t q[kMaxCols * kHeadDim];                    // Q digit planes, K-major: core (n/8)*8 + pos/16
     float cb[2][16];
-    float qf[kHeadsPerCta];                            // q unscale * sm_scale * log2(e) per head
-    float red_m[4][kHeadsPerCta];                      // cross-warp reductions
-    float red_l[4][kHeadsPerCta];
+    float qf[32];                                      // per (head of the tile, query head): q unscale * sm_scale * log2(e)
+    float mref[32];                                    // reference maxima, kept by the first lane of every head
+    float alpha[32];                                   // rescale factors of a moved reference
+    float red_m[8][kQPerHead];                         // per half warp (16 pairs of one head)
+    float red_l[8][kQPerHead];
     int scan[4];
-    uint64_t full[kStages];                            // "rows of the tile landed"
+    uint64_t full[kMaxStages];                         // "the tile's rows landed"
     uint64_t kready, pvready;                          // compute -> issuer: operands published (128 arrivals)
     uint64_t bar_s, bar_o, bar_drain;                  // issuer -> compute: MMAs complete
     uint32_t tmem_base;
     int grow_tile, redo_tile, dead;
     int32_t prefix[kInlinePlanSeqs + 1];
+    alignas(1024) uint8_t ring[kRingBytes];            // stages of [region][token][bytes]
+};
+
+struct TmaMaps {
+    CUtensorMap m[kRegions];
 };
 
 // Position on the line of tiles: walks the parts (piece x sequence) of one piece.
@@ -334,26 +380,22 @@ __device__ __forceinline__ int find_seq(const int32_t* prefix, int n, int64_t x)
     return lo;
 }
 
-// NH = query heads computed per item: 4 when the GQA group has at most 4 heads, else 8.
-template <typename T, int KB, int VB, int MODE, int NH>
-__global__ void __launch_bounds__(kDecodeThreads, DecodeSmem<MODE>::kCtasPerSm)
-decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v) {
-    using Smem = DecodeSmem<MODE>;
-    constexpr int S = Smem::kStages;
-    constexpr int VP = Smem::kVPitch;
+// NH = query heads computed per KV head: 4 when the GQA group has at most 4 heads, else 8.
+template <typename T, int KB, int VB, int NH>
+__global__ void __launch_bounds__(kDecodeThreads, kCtasPerSm)
+decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
     extern __shared__ uint8_t smem_raw[];
-    Smem& sm = *reinterpret_cast<Smem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
+    DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
     constexpr int NK = 1 << KB, NV = 1 << VB;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int J = p.H * p.head_groups;
+    const int J = (p.H >> p.ht_shift) * p.head_groups;
     const int64_t group = blockIdx.x / J;
     const int item = static_cast<int>(blockIdx.x % J);
+    const int S = p.stages;
 
-    // ---- set-up: barriers, tensor memory, codebooks, tile prefix sums ----
+    // ---- set-up: barriers, tensor memory, codebooks, tile prefix sums, a zero P tile ----
     if (tid == 0) {
-#pragma unroll
-        for (int s = 0; s < S; ++s) mbar_init(&sm.full[s], 1);
+        for (int s = 0; s < kMaxStages; ++s) mbar_init(&sm.full[s], p.box_rows > 0 ? 1 : 32);
         mbar_init(&sm.kready, kComputeThreads);
         mbar_init(&sm.pvready, kComputeThreads);
         mbar_init(&sm.bar_s, 1);
@@ -363,8 +405,11 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         sm.redo_tile = -1;
         sm.dead = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        fence_async_proxy();
     }
+    // P columns a pair never writes (the other KV head's half of its 16 columns) must read as zero
+    for (int i = tid; i < kPairs * 16 * 2 / 16; i += kDecodeThreads)
+        reinterpret_cast<uint4*>(sm.p)[i] = make_uint4(0u, 0u, 0u, 0u);
+    fence_async_proxy();
     if (warp == 0) tmem_alloc(&sm.tmem_base, kTmemCols);
     if (warp == kIssuerWarp) {
         const int kv = lane >> 4, i = lane & 15;
@@ -377,8 +422,8 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         int a = 0, b = 0;
         if (tid < kComputeThreads) {
             const int s0 = 2 * tid;
-            if (s0 < p.num_seqs) a = (max(__ldg(p.seq_lens + s0), 0) + kTileTokens - 1) / kTileTokens;
-            if (s0 + 1 < p.num_seqs) b = (max(__ldg(p.seq_lens + s0 + 1), 0) + kTileTokens - 1) / kTileTokens;
+            if (s0 < p.num_seqs) a = (max(__ldg(p.seq_lens + s0), 0) + p.ttok - 1) >> p.ttok_shift;
+            if (s0 + 1 < p.num_seqs) b = (max(__ldg(p.seq_lens + s0 + 1), 0) + p.ttok - 1) >> p.ttok_shift;
         }
         int incl = a + b;
 #pragma unroll
@@ -412,60 +457,63 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     const int64_t x_end = piece_begin(p, group + 1, total, J);
     const bool has_work = group < p.groups && x0 < x_end;
 
-    const SlotLayout lay = slot_layout(p.H);
-    const int kvh = item / p.head_groups, hg = item % p.head_groups;
-    const int heads_here = min(kHeadsPerCta, p.G - hg * kHeadsPerCta);
-    const int first_qh = kvh * p.G + hg * kHeadsPerCta;
-    // V rows: byte offset of the row inside the slot, rounded down to a 16-byte boundary for the copy
-    const int v_row = lay.v_idx + kvh * kHalfDim;
-    const int v_copy_x = MODE == 1 ? v_row : (v_row & ~15);
-    const int v_off = v_row - v_copy_x;                       // 0, 4, 8 or 12
+    const int hg = item % p.head_groups;
+    const int h0 = (item / p.head_groups) << p.ht_shift;            // first KV head of this CTA's head tile
+    const int heads_here = min(kQPerHead, p.G - hg * kQPerHead);     // query heads per KV head handled here
     const int last_blk = static_cast<int>(p.num_blocks) - 1;
+    const RegionWindow rw = region_window(p.H, h0);
+
+    auto start_walk = [&](Walk& w) {
+        w.x = x0;
+        w.seq = find_seq(prefix, p.num_seqs, x0);
+        const int pre = prefix[w.seq];
+        w.tile = static_cast<int>(x0 - pre);
+        const int64_t reach = w.tile + (x_end - x0);
+        const int n_s = prefix[w.seq + 1] - pre;
+        w.t_end = reach < n_s ? static_cast<int>(reach) : n_s;
+    };
+    // returns true when the new position is the first tile of a part
+    auto advance = [&](Walk& w) -> bool {
+        ++w.x;
+        ++w.tile;
+        if (w.tile < w.t_end || w.x >= x_end) return false;
+        do { ++w.seq; } while (w.seq < p.num_seqs - 1 && prefix[w.seq + 1] - prefix[w.seq] <= 0);
+        const int n_s = prefix[w.seq + 1] - prefix[w.seq];
+        const int64_t left = x_end - w.x;
+        w.tile = 0;
+        w.t_end = left < n_s ? static_cast<int>(left) : n_s;
+        return true;
+    };
 
     bool dead = false;
+#ifdef RQ_DECODE_TRACE
+    // CTAs 0, 100 and 200: [cta][warp][tile][16 points]
+    unsigned long long* trace_row = nullptr;
+    if (p.trace != nullptr && blockIdx.x % 100 == 0 && blockIdx.x / 100 < 3)
+        trace_row = p.trace + ((blockIdx.x / 100) * 5 + warp) * 64 * 16;
+#endif
 
     if (has_work && warp == kIssuerWarp) {
         // =========================== issuer warp ===========================
-        const uint32_t idesc_s = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+        const uint32_t ncols = static_cast<uint32_t>(p.n_cols);
+        const uint32_t idesc_s = (2u << 4) | (1u << 7) | (1u << 10) | ((ncols >> 3) << 17) | ((128u >> 4) << 24);
         const uint32_t idesc_o = (1u << 4) | (TcFormat<T>::kFmt << 7) | (TcFormat<T>::kFmt << 10) | (1u << 15) |
                                  (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
         const uint32_t q_addr = smem_u32(sm.q), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p);
-
-        auto start_walk = [&](Walk& w) {
-            w.x = x0;
-            w.seq = find_seq(prefix, p.num_seqs, x0);
-            const int pre = prefix[w.seq];
-            w.tile = static_cast<int>(x0 - pre);
-            const int64_t reach = w.tile + (x_end - x0);
-            const int n_s = prefix[w.seq + 1] - pre;
-            w.t_end = reach < n_s ? static_cast<int>(reach) : n_s;
-        };
-        // returns true when the new position is the first tile of a part
-        auto advance = [&](Walk& w) -> bool {
-            ++w.x;
-            ++w.tile;
-            if (w.tile < w.t_end || w.x >= x_end) return false;
-            do { ++w.seq; } while (w.seq < p.num_seqs - 1 && prefix[w.seq + 1] - prefix[w.seq] <= 0);
-            const int n_s = prefix[w.seq + 1] - prefix[w.seq];
-            const int64_t left = x_end - w.x;
-            w.tile = 0;
-            w.t_end = left < n_s ? static_cast<int>(left) : n_s;
-            return true;
-        };
+        const uint32_t ring_addr = smem_u32(sm.ring);
 
         // ---- producer: the rows of one tile into ring stage (n % S) ----
-        // The sequence length and this lane's block-table entry of the tile to be produced next are
-        // loaded right after the previous tile was issued, so that no load latency sits between the
-        // moment a stage becomes free and the copies into it.
+        // Lane b keeps the block-table entry of box b of the tile to be produced next, loaded right
+        // after the previous tile was issued.
         Walk pw;
         start_walk(pw);
         int produced = 0;
         int p_seq_len = max(__ldg(p.seq_lens + pw.seq), 0);
         int p_blk = 0;
         auto prefetch_blk = [&]() {
-            if constexpr (MODE != 0) {
-                const int t = pw.tile * kTileTokens + lane * p.box_tokens;
-                p_blk = (pw.x < x_end && lane * p.box_tokens < kTileTokens && t < p_seq_len)
+            if (p.box_rows > 0 && pw.x < x_end) {
+                const int t = (pw.tile << p.ttok_shift) + lane * p.box_rows;
+                p_blk = (lane * p.box_rows < p.ttok && t < p_seq_len)
                             ? __ldg(p.block_table + pw.seq * p.bt_stride + (t >> p.bs_shift)) : 0;
             }
         };
@@ -473,36 +521,43 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         auto produce = [&]() {
             const int stage = produced % S;
             const uint32_t bar = smem_u32(&sm.full[stage]);
-            const int tok0 = pw.tile * kTileTokens;
-            const int n_valid = min(kTileTokens, p_seq_len - tok0);
-            const uint32_t k_dst = smem_u32(sm.ring_k[stage]), v_dst = smem_u32(sm.ring_v[stage]);
-            if constexpr (MODE != 0) {
-                const int bt_tok = p.box_tokens;                  // 16 or 8: at most 16 boxes, one per lane
-                const int n_box = (n_valid + bt_tok - 1) / bt_tok;
-                const uint32_t box_bytes = static_cast<uint32_t>(bt_tok) * (kHalfDim + VP);
-                if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_box) * box_bytes);
+            const uint32_t dst0 = ring_addr + static_cast<uint32_t>(stage * p.stage_bytes);
+            const int tok0 = pw.tile << p.ttok_shift;
+            const int n_valid = min(p.ttok, p_seq_len - tok0);
+            if (p.box_rows > 0) {
+                const int n_box = (n_valid + p.box_rows - 1) / p.box_rows;       // at most 16: one per lane
+                int row_bytes = 0;
+                for (int r = 0; r < p.n_regions; ++r) row_bytes += p.reg_w[r];
+                if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_box * p.box_rows * row_bytes));
                 __syncwarp();
                 if (lane < n_box) {
-                    const int t = tok0 + lane * bt_tok;
+                    const int t = tok0 + lane * p.box_rows;
                     const int blk = p_blk < 0 ? 0 : (p_blk > last_blk ? last_blk : p_blk);
                     const int slot = (blk << p.bs_shift) + (t & (p.block_size - 1));
-                    tma_load_2d(k_dst + static_cast<uint32_t>(lane * bt_tok) * kHalfDim, &map_k, kvh * kHalfDim, slot, bar);
-                    tma_load_2d(v_dst + static_cast<uint32_t>(lane * bt_tok) * VP, &map_v, v_copy_x, slot, bar);
+#pragma unroll
+                    for (int r = 0; r < kRegions; ++r)
+                        if (r < p.n_regions)
+                            tma_load_2d(dst0 + p.reg_base[r] + lane * p.box_rows * p.reg_w[r], &maps.m[r],
+                                        (p.n_regions == 1 ? 0 : rw.x[r]) >> 3, slot, bar);
                 }
             } else {
+                // any block size: 4-byte copies of every region's window, token by token
                 const int32_t* bt_row = p.block_table + pw.seq * p.bt_stride;
-                if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_valid) * (kHalfDim + VP));
-                __syncwarp();
-                for (int i = lane; i < n_valid; i += 32) {
-                    const int t = tok0 + i;
-                    const int bi = p.bs_shift >= 0 ? (t >> p.bs_shift) : (t / p.block_size);
-                    const int off = p.bs_shift >= 0 ? (t & (p.block_size - 1)) : (t % p.block_size);
-                    int blk = __ldg(bt_row + bi);
-                    blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
-                    const uint8_t* slot = p.cache + (static_cast<int64_t>(blk) * p.block_size + off) * p.total_bytes;
-                    bulk_load(k_dst + static_cast<uint32_t>(i) * kHalfDim, slot + kvh * kHalfDim, kHalfDim, bar);
-                    bulk_load(v_dst + static_cast<uint32_t>(i) * VP, slot + v_copy_x, VP, bar);
+                for (int r = 0; r < p.n_regions; ++r) {
+                    const int words = p.reg_w[r] >> 2;
+                    const int src_x = p.n_regions == 1 ? 0 : rw.x[r];
+                    for (int i = lane; i < n_valid * words; i += 32) {
+                        const int tt = i / words, wd = i - tt * words;
+                        const int t = tok0 + tt;
+                        const int bi = p.bs_shift >= 0 ? (t >> p.bs_shift) : (t / p.block_size);
+                        const int off = p.bs_shift >= 0 ? (t & (p.block_size - 1)) : (t % p.block_size);
+                        int blk = __ldg(bt_row + bi);
+                        blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
+                        const uint8_t* slot = p.cache + (static_cast<int64_t>(blk) * p.block_size + off) * p.total_bytes;
+                        cp_async4(dst0 + p.reg_base[r] + tt * p.reg_w[r] + 4 * wd, slot + src_x + 4 * wd);
+                    }
                 }
+                cp_async_arrive(&sm.full[stage]);
             }
             __syncwarp();
             ++produced;
@@ -518,10 +573,13 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         bool first_in_part = true;
         uint32_t ph_pv = 0;
         int it = 0;
+        const int cols_per_head = 2 * NH;
 #pragma unroll 1
         for (; cw.x < x_end; ++it) {
             // S^T = K Q^T: the digit planes of the tile are in tensor memory, the query planes in shared memory
+            RQ_TRACE(0);
             if (!mbar_wait(&sm.kready, it & 1)) { dead = true; break; }
+            RQ_TRACE(1);
             tc_fence_after();
             if (lane == 0) {
 #pragma unroll
@@ -530,13 +588,15 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                                  idesc_s, s > 0 ? 1u : 0u);
 #pragma unroll
                 for (int s = 0; s < 4; ++s)
-                    tc_mma_i8_ta(tmem + kColS + 16, tmem + kColKlo + 8 * s, smem_desc(q_addr + 256 * s, 128, 1024),
+                    tc_mma_i8_ta(tmem + kColS2, tmem + kColKlo + 8 * s, smem_desc(q_addr + 256 * s, 128, 1024),
                                  idesc_s, s > 0 ? 1u : 0u);
                 tc_commit(&sm.bar_s);
             }
             __syncwarp();
-            // O^T += V^T [P hi | P lo]
+            RQ_TRACE(2);
+            // O^T += V^T [P hi | P lo], one k-step of 16 pairs (one KV head) at a time
             if (!mbar_wait(&sm.pvready, ph_pv)) { dead = true; break; }
+            RQ_TRACE(3);
             ph_pv ^= 1u;
             if (ld_volatile_shared(&sm.grow_tile) == it) {
                 // a score outgrew the reference maximum: hand the tile back; the compute warps move the
@@ -551,31 +611,54 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             }
             tc_fence_after();
             if (lane == 0) {
+                int prev_blk = -1;
 #pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    tc_mma_f16(tmem + kColO, smem_desc(v_addr + 4096 * s, 2048, 128),
-                               smem_desc(p_addr + 512 * s, 256, 128), idesc_o, (!first_in_part || s > 0) ? 1u : 0u);
+                for (int s = 0; s < 8; ++s) {
+                    // output columns of the KV head of pairs 16 s .. 16 s + 15, as a block of 16
+                    const int blk16 = (((16 * s) >> p.ttok_shift) * cols_per_head) >> 4;
+                    const uint32_t acc = (first_in_part && blk16 != prev_blk) ? 0u : 1u;
+                    prev_blk = blk16;
+                    tc_mma_f16(tmem + kColO + 16 * blk16, smem_desc(v_addr + 4096 * s, 2048, 128),
+                               smem_desc(p_addr + 512 * s, 256, 128), idesc_o, acc);
+                }
                 tc_commit(&sm.bar_o);
             }
             __syncwarp();
+            RQ_TRACE(4);
             // every compute thread has read its rows of this tile's stage: refill it
             if (pw.x < x_end) produce();
+            RQ_TRACE(5);
             first_in_part = advance(cw);
         }
         if (dead) {
             st_volatile_shared(&sm.dead, 1);
             // copies still in flight: a bounded wait each, so that none lands after the CTA is gone
-            for (int c = it; c < produced; ++c) mbar_wait(&sm.full[c % S], (c / S) & 1);
+            if (p.box_rows > 0)
+                for (int c = it; c < produced; ++c) mbar_wait(&sm.full[c % S], (c / S) & 1);
             if (lane == 0) tc_commit(&sm.bar_drain);
             __syncwarp();
             mbar_wait(&sm.bar_drain, 0);
         }
+        cp_async_wait_all();
     } else if (has_work) {
         // =========================== compute warps ===========================
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lane quarter
         uint8_t* const v_dst = reinterpret_cast<uint8_t*>(sm.v) + (tid >> 3) * (16 * 128) + (tid & 7) * 16;
-        uint8_t* const p_dst = reinterpret_cast<uint8_t*>(sm.p) + (tid >> 3) * (2 * 128) + (tid & 7) * 16;
-        const uint32_t k_sw = MODE != 0 ? 16u * ((tid >> 1) & 3) : 0u;      // swizzle of this token's row
+        const int hh = tid >> p.ttok_shift, tt = tid & (p.ttok - 1);      // this pair: KV head of the tile, token
+        const int half = tid >> 4;                                         // 16 pairs of one head
+        const int halves_per_head = p.ttok >> 4, first_half = (half / halves_per_head) * halves_per_head;
+        const int col16 = (hh * 2 * NH) & ~15, sub = (hh * 2 * NH) & 15;   // this head's columns: block of 16, offset
+        // P: this pair's row of 16 columns; with 4 query heads its 8 values fill one 8-column core
+        uint8_t* const p_dst = reinterpret_cast<uint8_t*>(sm.p) + (tid >> 3) * (2 * 128) + (tid & 7) * 16 +
+                               (NH == 4 ? (sub >> 3) * 128 : 0);
+        // where this pair's bytes sit inside a stage
+        int f_off[kRegions];
+#pragma unroll
+        for (int r = 0; r < kRegions; ++r) {
+            const int unit = (r & 1) ? 4 : kHalfDim;
+            f_off[r] = p.n_regions == 1 ? tt * p.reg_w[0] + rw.start[r] + unit * hh
+                                        : p.reg_base[r] + tt * p.reg_w[r] + (rw.start[r] - rw.x[r]) + unit * hh;
+        }
         float cmax_k = 0.0f;
 #pragma unroll
         for (int i = 0; i < NK; ++i) cmax_k = fmaxf(cmax_k, fabsf(sm.cb[0][i]));
@@ -593,50 +676,28 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             const int64_t reach = t_begin + (x_end - x);
             const int t_end = reach < n_s ? static_cast<int>(reach) : n_s;
             const int seq_len = max(__ldg(p.seq_lens + seq), 0);
-            const int32_t* bt_row = p.block_table + seq * p.bt_stride;
-
-            // Norms of this thread's token: fetched one tile ahead, the block-table entry two tiles ahead.
-            auto load_blk = [&](int tile) -> int {
-                const int tok = tile * kTileTokens + tid;
-                if (tile >= t_end || tok >= seq_len) return -1;
-                const int bi = p.bs_shift >= 0 ? (tok >> p.bs_shift) : (tok / p.block_size);
-                const int blk = __ldg(bt_row + bi);
-                return blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
-            };
-            auto load_norms = [&](int tile, int blk, float& nk, float& nv) {
-                nk = 0.0f;
-                nv = 0.0f;                           // zero norms make every table entry zero
-                if (blk >= 0) {
-                    const int tok = tile * kTileTokens + tid;
-                    const int off = p.bs_shift >= 0 ? (tok & (p.block_size - 1)) : (tok % p.block_size);
-                    const uint8_t* slot = p.cache + (static_cast<int64_t>(blk) * p.block_size + off) * p.total_bytes;
-                    nk = __ldg(reinterpret_cast<const float*>(slot + lay.k_norm + 4 * kvh));
-                    nv = __ldg(reinterpret_cast<const float*>(slot + lay.v_norm + 4 * kvh));
-                }
-            };
-            float nk, nv, nk_next = 0.0f, nv_next = 0.0f;
-            load_norms(t_begin, load_blk(t_begin), nk, nv);
-            int blk_next = load_blk(t_begin + 1);
 
             // ---- queries of this part: rotate, round, quantise to signed digit planes (B operand) ----
+            // rows of head j of the tile: 2 NH j + g (high digits of query head g), 2 NH j + NH + g (low digits)
 #pragma unroll 1
-            for (int round = 0; round < NH / 4; ++round) {
-                const int h = 4 * round + warp;
+            for (int jq = warp; jq < (NH << p.ht_shift); jq += 4) {
+                const int j = jq / NH, g = jq % NH;
                 float r[4] = {0.f, 0.f, 0.f, 0.f};
-                if (h < heads_here) {
+                if (g < heads_here) {
+                    const int qh = (h0 + j) * p.G + hg * kQPerHead + g;
                     const T* qp = static_cast<const T*>(p.q) + seq * p.q_stride_seq +
-                                  static_cast<int64_t>(first_qh + h) * p.q_stride_head + 4 * lane;
+                                  static_cast<int64_t>(qh) * p.q_stride_head + 4 * lane;
                     const uint2 raw = __ldg(reinterpret_cast<const uint2*>(qp));
                     const float2 x01 = unpack_pair<T>(raw.x), x23 = unpack_pair<T>(raw.y);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int k = 0; k < 4; ++k) {
                         const float4 rr = __ldg(reinterpret_cast<const float4*>(
-                            p.rotation + (4 * lane + j) * kHeadDim + 4 * lane));
+                            p.rotation + (4 * lane + k) * kHeadDim + 4 * lane));
                         float acc = __fmul_rn(x01.x, rr.x);
                         acc = __fmaf_rn(x01.y, rr.y, acc);
                         acc = __fmaf_rn(x23.x, rr.z, acc);
                         acc = __fmaf_rn(x23.y, rr.w, acc);
-                        r[j] = round_to<T>(acc);
+                        r[k] = round_to<T>(acc);
                     }
                 }
                 float mx = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
@@ -647,50 +708,62 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 const float scale = ok ? pow2i(13 - e) : 0.0f;
                 int qu[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) qu[j] = __float2int_rn(fmaf(r[j], scale, 128.0f));
+                for (int k = 0; k < 4; ++k) qu[k] = __float2int_rn(fmaf(r[k], scale, 128.0f));
                 // position x of a row holds head-dim x ^ 1 (the nibble order of the cache)
                 const uint32_t a = prmt(qu[1], qu[0], 0x5140), b = prmt(qu[3], qu[2], 0x5140);
-                const uint32_t off = (lane >> 2) * 128 + (h & 7) * 16 + 4 * (lane & 3);
-                *reinterpret_cast<uint32_t*>(&sm.q[off]) = prmt(a, b, 0x7632);                       // row h: high digits
-                *reinterpret_cast<uint32_t*>(&sm.q[1024 + off]) = prmt(a, b, 0x5410) ^ 0x80808080u;  // row 8 + h: low digits
-                if (lane == 0) sm.qf[h] = (ok ? pow2i(e - 13) : 0.0f) * p.qk_scale;
+                const int row_hi = 2 * NH * j + g, row_lo = row_hi + NH;
+                const uint32_t in_row = (lane >> 2) * 128 + 4 * (lane & 3);
+                *reinterpret_cast<uint32_t*>(&sm.q[(row_hi >> 3) * 1024 + (row_hi & 7) * 16 + in_row]) = prmt(a, b, 0x7632);
+                *reinterpret_cast<uint32_t*>(&sm.q[(row_lo >> 3) * 1024 + (row_lo & 7) * 16 + in_row]) =
+                    prmt(a, b, 0x5410) ^ 0x80808080u;
+                if (lane == 0) sm.qf[NH * j + g] = (ok ? pow2i(e - 13) : 0.0f) * p.qk_scale;
             }
             fence_async_proxy();
             compute_sync();
 
-            float m_ref[NH], l_acc[NH], l_pend[NH], sc[NH];
+            float m_ref[NH], l_acc[NH], l_pend[NH], sc[NH], qfk[NH];
 #pragma unroll
-            for (int h = 0; h < NH; ++h) { m_ref[h] = -INFINITY; l_acc[h] = 0.0f; l_pend[h] = 0.0f; sc[h] = 0.0f; }
+            for (int g = 0; g < NH; ++g) {
+                m_ref[g] = -INFINITY; l_acc[g] = 0.0f; l_pend[g] = 0.0f; sc[g] = 0.0f;
+                qfk[g] = sm.qf[NH * hh + g];
+            }
             bool pending = false;                    // a P V of this part has been requested and not yet awaited
 
             // probabilities of the tile whose scores are in sc[], against the current reference maxima
             auto emit_p = [&]() {
-                uint32_t ph[4] = {0u, 0u, 0u, 0u}, pl[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                for (int h = 0; h < NH; ++h) l_pend[h] = ex2_approx(sc[h] - m_ref[h]);
+                for (int g = 0; g < NH; ++g) l_pend[g] = ex2_approx(sc[g] - m_ref[g]);
+                uint32_t ph[NH / 2], pl[NH / 2];
 #pragma unroll
                 for (int j = 0; j < NH / 2; ++j) {
                     ph[j] = pack_pair<T>(l_pend[2 * j], l_pend[2 * j + 1]);
                     const float2 back = unpack_pair<T>(ph[j]);
                     pl[j] = pack_pair<T>(l_pend[2 * j] - back.x, l_pend[2 * j + 1] - back.y);
                 }
-                *reinterpret_cast<uint4*>(p_dst) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                *reinterpret_cast<uint4*>(p_dst + 128) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                if constexpr (NH == 4) {
+                    *reinterpret_cast<uint4*>(p_dst) = make_uint4(ph[0], ph[1], pl[0], pl[1]);
+                } else {
+                    *reinterpret_cast<uint4*>(p_dst) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                    *reinterpret_cast<uint4*>(p_dst + 128) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                }
                 fence_async_proxy();
             };
-            // CTA-wide maximum of sc[] per head -> m_new[]
-            auto tile_max = [&](float (&m_new)[NH]) {
+            // maximum of sc[] over the pairs of this thread's KV head -> m_new[]
+            auto head_max = [&](float (&m_new)[NH]) {
 #pragma unroll
-                for (int h = 0; h < NH; ++h) {
-                    float m = sc[h];
+                for (int g = 0; g < NH; ++g) {
+                    float m = sc[g];
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                    if (lane == 0) sm.red_m[warp][h] = m;
+                    for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                    if ((lane & 15) == 0) sm.red_m[half][g] = m;
                 }
                 compute_sync();
 #pragma unroll
-                for (int h = 0; h < NH; ++h)
-                    m_new[h] = fmaxf(fmaxf(sm.red_m[0][h], sm.red_m[1][h]), fmaxf(sm.red_m[2][h], sm.red_m[3][h]));
+                for (int g = 0; g < NH; ++g) {
+                    float m = sm.red_m[first_half][g];
+                    for (int i = 1; i < halves_per_head; ++i) m = fmaxf(m, sm.red_m[first_half + i][g]);
+                    m_new[g] = m;
+                }
                 compute_sync();                      // red_m may be rewritten from here on
             };
             // Wait for the P V of tile `it - 1`; if the issuer handed the tile back because a score
@@ -701,23 +774,29 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 tc_fence_after();
                 if (ld_volatile_shared(&sm.redo_tile) == it - 1) {
                     float m_new[NH];
-                    tile_max(m_new);
-                    uint32_t o[16];
-                    tmem_ld16_nowait(lane_base + kColO, o);          // lane = head-dim, column = head (hi | lo)
-                    float alpha[kHeadsPerCta];
+                    head_max(m_new);
 #pragma unroll
-                    for (int h = NH; h < kHeadsPerCta; ++h) alpha[h] = 1.0f;
-#pragma unroll
-                    for (int h = 0; h < NH; ++h) {
-                        m_new[h] = fmaxf(m_new[h], m_ref[h]);
-                        alpha[h] = ex2_approx(m_ref[h] - m_new[h]);
-                        l_acc[h] *= alpha[h];
-                        m_ref[h] = m_new[h];
+                    for (int g = 0; g < NH; ++g) {
+                        m_new[g] = fmaxf(m_new[g], m_ref[g]);
+                        const float a = ex2_approx(m_ref[g] - m_new[g]);
+                        l_acc[g] *= a;
+                        m_ref[g] = m_new[g];
+                        if (tt == 0) { sm.alpha[NH * hh + g] = a; sm.mref[NH * hh + g] = m_new[g]; }
                     }
-                    tmem_wait_ld();
+                    compute_sync();
+                    // O^T: lane = head-dim, column 2 NH j + g (+ NH: the lo part) = query head g of head j
+                    for (int c0 = 0; c0 < p.n_cols; c0 += 16) {
+                        uint32_t o[16];
+                        tmem_ld16_nowait(lane_base + kColO + c0, o);
+                        tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c & 7]);
-                    tmem_st16_nowait(lane_base + kColO, o);
+                        for (int c = 0; c < 16; ++c) {
+                            const int col = c0 + c, j = col / (2 * NH), g = col % NH;
+                            const float a = j < p.ht ? sm.alpha[NH * j + g] : 1.0f;
+                            o[c] = __float_as_uint(__uint_as_float(o[c]) * a);
+                        }
+                        tmem_st16_nowait(lane_base + kColO + c0, o);
+                    }
                     tmem_wait_st();
                     emit_p();
                     tc_fence_before();
@@ -727,29 +806,30 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                     tc_fence_after();
                 }
 #pragma unroll
-                for (int h = 0; h < NH; ++h) l_acc[h] += l_pend[h];
+                for (int g = 0; g < NH; ++g) l_acc[g] += l_pend[g];
                 pending = false;
             };
 
 #pragma unroll 1
             for (int tile = t_begin; tile < t_end; ++tile, ++it) {
                 const int stage = it % S;
-                const bool valid = tile * kTileTokens + tid < seq_len;
-                // next tile's norms are requested now and used a tile later; its block-table entry was
-                // loaded a tile ago
-                load_norms(tile + 1, blk_next, nk_next, nv_next);
-                blk_next = load_blk(tile + 2);
+                const bool valid = (tile << p.ttok_shift) + tt < seq_len;
+                const uint8_t* stg = sm.ring + stage * p.stage_bytes;
+                RQ_TRACE(0);
                 if (!mbar_wait(&sm.full[stage], (it / S) & 1)) { dead = true; break; }
+                RQ_TRACE(1);
 
                 // ---- K table, digit planes -> tensor memory ----
                 float k_unscale;
                 {
+                    // a zero norm makes every table entry zero: pairs past the end contribute nothing
+                    const float nk = valid ? *reinterpret_cast<const float*>(stg + f_off[1]) : 0.0f;
                     const Table<KB> tk = build_int_table<T, KB>(sm.cb[0], cmax_k, nk, k_unscale);
-                    const uint8_t* krow = sm.ring_k[stage] + tid * kHalfDim;
+                    const uint8_t* krow = stg + f_off[0];
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const uint4 w0 = *reinterpret_cast<const uint4*>(krow + ((32u * half) ^ k_sw));
-                        const uint4 w1 = *reinterpret_cast<const uint4*>(krow + ((32u * half + 16u) ^ k_sw));
+                    for (int hf = 0; hf < 2; ++hf) {
+                        const uint4 w0 = *reinterpret_cast<const uint4*>(krow + 32 * hf);
+                        const uint4 w1 = *reinterpret_cast<const uint4*>(krow + 32 * hf + 16);
                         const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
                         uint32_t hi[16], lo[16];
 #pragma unroll
@@ -757,22 +837,25 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                             lookup4<KB>(tk, words[w], lo[2 * w], hi[2 * w]);
                             lookup4<KB>(tk, words[w] >> 16, lo[2 * w + 1], hi[2 * w + 1]);
                         }
-                        tmem_st16_nowait(lane_base + kColKhi + 16 * half, hi);
-                        tmem_st16_nowait(lane_base + kColKlo + 16 * half, lo);
+                        tmem_st16_nowait(lane_base + kColKhi + 16 * hf, hi);
+                        tmem_st16_nowait(lane_base + kColKlo + 16 * hf, lo);
                     }
                 }
+                RQ_TRACE(2);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&sm.kready);
+                RQ_TRACE(3);
 
                 // ---- V row -> shared tile (the previous tile's P V must have read it) ----
                 if (pending) {
                     settle_pending();
                     if (dead) break;
                 }
-                uint32_t d[32];                              // the 32 sums of this token
+                RQ_TRACE(4);
+                uint32_t d1[16], d2[16];                     // this pair's sums: 16 columns of each accumulator
                 {
-                    Table<VB> tb = build_value_table<T, VB>(sm.cb[1], nv);
+                    Table<VB> tb = build_value_table<T, VB>(sm.cb[1], *reinterpret_cast<const float*>(stg + f_off[3]));
                     if (!valid) {
                         // rows past the end of the sequence may hold bytes that are not index nibbles; with an
                         // all-zero table every PRMT result is zero whatever the selector (a -0.0 entry would
@@ -780,24 +863,27 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
 #pragma unroll
                         for (int r = 0; r < Table<VB>::kRegs; ++r) tb.r[r] = 0u;
                     }
-                    const uint8_t* vrow = sm.ring_v[stage] + tid * VP;
+                    const uint8_t* vrow = stg + f_off[2];
 #pragma unroll
                     for (int quarter = 0; quarter < 4; ++quarter) {
                         if (quarter == 2) {
-                            // S^T is normally complete by now: request this token's sums so that the
+                            // S^T is normally complete by now: request this pair's sums so that the
                             // tensor-memory read runs under the second half of the V row
+                            RQ_TRACE(5);
                             if (!mbar_wait(&sm.bar_s, it & 1)) { dead = true; break; }
+                            RQ_TRACE(6);
                             tc_fence_after();
-                            tmem_ld32_nowait(lane_base + kColS, d);
+                            tmem_ld16_nowait(lane_base + kColS + col16, d1);
+                            tmem_ld16_nowait(lane_base + kColS2 + col16, d2);
                         }
                         uint32_t words[4];
-                        if constexpr (MODE == 1) {
-                            const uint4 w4 = *reinterpret_cast<const uint4*>(vrow + ((16u * quarter) ^ k_sw));
+                        if (p.v_aligned) {
+                            const uint4 w4 = *reinterpret_cast<const uint4*>(vrow + 16 * quarter);
                             words[0] = w4.x; words[1] = w4.y; words[2] = w4.z; words[3] = w4.w;
                         } else {
 #pragma unroll
                             for (int w = 0; w < 4; ++w)
-                                words[w] = *reinterpret_cast<const uint32_t*>(vrow + v_off + 16 * quarter + 4 * w);
+                                words[w] = *reinterpret_cast<const uint32_t*>(vrow + 16 * quarter + 4 * w);
                         }
 #pragma unroll
                         for (int w = 0; w < 4; ++w) {          // 8 head-dims = one 32-bit index word per chunk
@@ -814,41 +900,53 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
 
                 // ---- scores, reference maxima, probabilities ----
                 const float tok_bias = valid ? 0.0f : -INFINITY;
+                RQ_TRACE(7);
                 {
                     tmem_wait_ld();
-                    tmem_ld32_landed(d);
-                    const float4 qf0 = *reinterpret_cast<const float4*>(&sm.qf[0]);
-                    const float4 qf1 = *reinterpret_cast<const float4*>(&sm.qf[4]);
-                    const float qf[8] = {qf0.x, qf0.y, qf0.z, qf0.w, qf1.x, qf1.y, qf1.z, qf1.w};
+                    RQ_TRACE(8);
+                    tmem_ld16_landed(d1);
+                    tmem_ld16_landed(d2);
 #pragma unroll
-                    for (int h = 0; h < NH; ++h) {
-                        // d[h] = Khi.Qhi, d[8+h] = Khi.Qlo, d[16+h] = Klo.Qhi, d[24+h] = Klo.Qlo
-                        const int t1 = static_cast<int>(d[h]) * 256 + (static_cast<int>(d[8 + h]) + static_cast<int>(d[16 + h]));
-                        const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(static_cast<int>(d[24 + h])));
-                        // heads beyond the group have factor 0: they behave like heads with all-zero scores and
-                        // their columns are never written out; tokens past the end get -inf (probability 0)
-                        sc[h] = fmaf(f, qf[h] * k_unscale, tok_bias);
+                    for (int g = 0; g < NH; ++g) {
+                        // columns of this head: sub + g = Q high digits of query head g, sub + NH + g = low digits
+                        int hh_, hl_, lh_, ll_;
+                        if constexpr (NH == 4) {
+                            hh_ = static_cast<int>(sub ? d1[8 + g] : d1[g]);
+                            hl_ = static_cast<int>(sub ? d1[12 + g] : d1[4 + g]);
+                            lh_ = static_cast<int>(sub ? d2[8 + g] : d2[g]);
+                            ll_ = static_cast<int>(sub ? d2[12 + g] : d2[4 + g]);
+                        } else {
+                            hh_ = static_cast<int>(d1[g]); hl_ = static_cast<int>(d1[8 + g]);
+                            lh_ = static_cast<int>(d2[g]); ll_ = static_cast<int>(d2[8 + g]);
+                        }
+                        const int t1 = hh_ * 256 + (hl_ + lh_);
+                        const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(ll_));
+                        // query heads beyond the group have factor 0: they behave like heads with all-zero scores
+                        // and their columns are never written out; pairs past the end get -inf (probability 0)
+                        sc[g] = fmaf(f, qfk[g] * k_unscale, tok_bias);
                     }
                 }
                 if (tile == t_begin) {
                     // first tile of the part: the reference maxima are the exact maxima of this tile
                     float m_new[NH];
-                    tile_max(m_new);
+                    head_max(m_new);
 #pragma unroll
-                    for (int h = 0; h < NH; ++h) m_ref[h] = m_new[h];
+                    for (int g = 0; g < NH; ++g) {
+                        m_ref[g] = m_new[g];
+                        if (tt == 0) sm.mref[NH * hh + g] = m_new[g];
+                    }
                 } else {
                     bool grow = false;
 #pragma unroll
-                    for (int h = 0; h < NH; ++h) grow |= sc[h] > m_ref[h] + 8.0f;
+                    for (int g = 0; g < NH; ++g) grow |= sc[g] > m_ref[g] + 8.0f;
                     // rare: ask the issuer to hand the tile back instead of issuing its P V
                     if (grow) st_volatile_shared(&sm.grow_tile, it);
                 }
                 emit_p();
                 tc_fence_before();
                 mbar_arrive(&sm.pvready);
+                RQ_TRACE(9);
                 pending = true;
-                nk = nk_next;
-                nv = nv_next;
             }
             if (dead) break;
 
@@ -858,31 +956,38 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
                 if (dead) break;
             }
 #pragma unroll
-            for (int h = 0; h < NH; ++h) {
-                float v = l_acc[h];
+            for (int g = 0; g < NH; ++g) {
+                float v = l_acc[g];
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) sm.red_l[warp][h] = v;
+                for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if ((lane & 15) == 0) sm.red_l[half][g] = v;
             }
             compute_sync();
             const int64_t row = (group + seq) * J + item;
-            if (tid < heads_here) {
-                float m = m_ref[0];
-#pragma unroll
-                for (int h = 1; h < NH; ++h) m = tid == h ? m_ref[h] : m;
-                const float l = (sm.red_l[0][tid] + sm.red_l[1][tid]) + (sm.red_l[2][tid] + sm.red_l[3][tid]);
-                p.ws_m[row * kHeadsPerCta + tid] = m;
-                p.ws_l[row * kHeadsPerCta + tid] = l;
+            const int slots = p.ht * kQPerHead;
+            if (tid < p.ht * NH) {
+                const int j = tid / NH, g = tid % NH;
+                if (g < heads_here) {
+                    float l = 0.0f;
+                    for (int i = 0; i < halves_per_head; ++i) l += sm.red_l[j * halves_per_head + i][g];
+                    p.ws_m[row * slots + j * kQPerHead + g] = sm.mref[NH * j + g];
+                    p.ws_l[row * slots + j * kQPerHead + g] = l;
+                }
             }
-            {
+            for (int c0 = 0; c0 < p.ht * 2 * NH; c0 += 16) {
                 uint32_t o[16];
-                tmem_ld16_nowait(lane_base + kColO, o);
+                tmem_ld16_nowait(lane_base + kColO + c0, o);
                 tmem_wait_ld();
 #pragma unroll
-                for (int h = 0; h < NH; ++h)               // lane (position) x holds head-dim x ^ 1
-                    if (h < heads_here)
-                        p.ws_o[(row * kHeadsPerCta + h) * kHeadDim + (tid ^ 1)] =
-                            __uint_as_float(o[h]) + __uint_as_float(o[8 + h]);
+                for (int c = 0; c < 16; ++c) {
+                    // columns come in groups of 2 NH per head: NH hi parts, then NH lo parts
+                    if ((c % (2 * NH)) < NH) {
+                        const int j = (c0 + c) / (2 * NH), g = c % NH;
+                        if (g < heads_here && j < p.ht)      // lane (position) x holds head-dim x ^ 1
+                            p.ws_o[((row * slots + j * kQPerHead + g) << 7) + (tid ^ 1)] =
+                                __uint_as_float(o[c]) + __uint_as_float(o[c + NH]);
+                    }
+                }
             }
             tc_fence_before();
             compute_sync();                          // red_l, the query planes and O^T are free for the next part
@@ -901,14 +1006,15 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         // (NaN row sum), which the merge turns into NaN outputs.
         int64_t x = x0;
         int seq = find_seq(prefix, p.num_seqs, x0);
+        const int slots = p.ht * kQPerHead;
         while (x < x_end && seq < p.num_seqs) {
             const int pre = prefix[seq], n_s = prefix[seq + 1] - pre;
             if (n_s <= 0 || x >= static_cast<int64_t>(pre) + n_s) { ++seq; continue; }
             const int64_t left = x_end - x, in_seq = static_cast<int64_t>(pre) + n_s - x;
             const int64_t row = (group + seq) * J + item;
-            if (tid < kHeadsPerCta) {
-                p.ws_m[row * kHeadsPerCta + tid] = 0.0f;
-                p.ws_l[row * kHeadsPerCta + tid] = __int_as_float(0x7fc00000);
+            if (tid < slots) {
+                p.ws_m[row * slots + tid] = 0.0f;
+                p.ws_l[row * slots + tid] = __int_as_float(0x7fc00000);
             }
             x += left < in_seq ? left : in_seq;
             ++seq;
@@ -918,15 +1024,16 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
 }
 
 // Tiles of every sequence as an exclusive prefix sum, for batches too large for the attention CTAs
-// to scan themselves: prefix[s] = sum_{s' < s} ceil(len[s'] / 128), prefix[num_seqs] = total.
-__global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num_seqs, int32_t* __restrict__ prefix) {
+// to scan themselves: prefix[s] = sum_{s' < s} ceil(len[s'] / tile_tokens), prefix[num_seqs] = total.
+__global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num_seqs, int tile_tokens,
+                                   int32_t* __restrict__ prefix) {
     __shared__ int warp_sums[32];
     __shared__ int carry;
     if (threadIdx.x == 0) carry = 0;
     __syncthreads();
     for (int base = 0; base < num_seqs; base += blockDim.x) {
         const int s = base + threadIdx.x;
-        const int n = s < num_seqs ? (max(__ldg(seq_lens + s), 0) + kTileTokens - 1) / kTileTokens : 0;
+        const int n = s < num_seqs ? (max(__ldg(seq_lens + s), 0) + tile_tokens - 1) / tile_tokens : 0;
         int incl = n;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -947,8 +1054,10 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num
 
 // Merge: one warp per (sequence, query head), lane l owns head-dims 4l..4l+3 (one 4x4 block of R).
 // The parts of a (sequence, head) are the groups whose pieces overlap the sequence's tile range;
-// part (group, sequence) of item j lives at row (group + sequence) * J + j.  Lanes gather the running
-// maxima and row sums of up to 32 parts at a time; then the warp sums the weighted partial outputs.
+// part (group, sequence) of item j lives at row (group + sequence) * J + j, and inside the row the
+// query head sits in slot (KV head within its tile) * 8 + (query head within its group of 8).  Lanes
+// gather the running maxima and row sums of up to 32 parts at a time; then the warp sums the
+// weighted partial outputs.
 constexpr int kMergeWarps = 4;
 template <typename T>
 __global__ void __launch_bounds__(kMergeWarps * 32)
@@ -958,9 +1067,11 @@ decode_merge_kernel(const DecodeParams p) {
     const int64_t wq = static_cast<int64_t>(blockIdx.x) * kMergeWarps + (threadIdx.x >> 5);
     if (wq >= static_cast<int64_t>(p.num_seqs) * p.Hq) return;
     const int seq = static_cast<int>(wq / p.Hq), qh = static_cast<int>(wq % p.Hq);
-    const int J = p.H * p.head_groups;
+    const int J = (p.H >> p.ht_shift) * p.head_groups;
     const int kvh = qh / p.G, hl = qh % p.G;
-    const int item = kvh * p.head_groups + hl / kHeadsPerCta, h = hl % kHeadsPerCta;
+    const int item = (kvh >> p.ht_shift) * p.head_groups + hl / kQPerHead;
+    const int slots = p.ht * kQPerHead;
+    const int slot = (kvh & (p.ht - 1)) * kQPerHead + hl % kQPerHead;
     const int64_t a = p.prefix[seq], n = p.prefix[seq + 1] - a, total = p.prefix[p.num_seqs];
 
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -986,7 +1097,7 @@ decode_merge_kernel(const DecodeParams p) {
             const int gi = g0 + lane;
             // groups whose piece is empty (only when there are more groups than tiles) wrote nothing
             const bool live = gi <= g_last && piece_begin(p, gi, total, J) < piece_begin(p, gi + 1, total, J);
-            const int64_t r = ((static_cast<int64_t>(gi) + seq) * J + item) * kHeadsPerCta + h;
+            const int64_t r = ((static_cast<int64_t>(gi) + seq) * J + item) * slots + slot;
             const float m = live ? p.ws_m[r] : -INFINITY;
             const float l = live ? p.ws_l[r] : 0.0f;
             float m_round = m;
@@ -1007,7 +1118,7 @@ decode_merge_kernel(const DecodeParams p) {
                 const float wk = __shfl_sync(0xffffffffu, w, k);
                 if (wk != 0.0f) {
                     const float4 o = *reinterpret_cast<const float4*>(
-                        p.ws_o + (((static_cast<int64_t>(g0 + k) + seq) * J + item) * kHeadsPerCta + h) * kHeadDim + 4 * lane);
+                        p.ws_o + ((((static_cast<int64_t>(g0 + k) + seq) * J + item) * slots + slot) << 7) + 4 * lane);
                     acc.x += wk * o.x; acc.y += wk * o.y; acc.z += wk * o.z; acc.w += wk * o.w;
                 }
             }
@@ -1045,6 +1156,10 @@ static int env_int(const char* name, int fallback) {
     return (e != nullptr && e[0] != '\0') ? std::atoi(e) : fallback;
 }
 
+#ifdef RQ_DECODE_TRACE
+static unsigned long long* g_trace_buffer = nullptr;
+#endif
+
 // SM count of the current device (148 on a B200), looked up once per device.
 static int sm_count() {
     static std::mutex mu;
@@ -1060,39 +1175,52 @@ static int sm_count() {
     return cached[dev];
 }
 
-// Grid and scratch of one decode call.  The (sequence, tile) space is cut into `groups` pieces;
-// each piece is walked by J CTAs, one per (KV head, head group).
+// Tile geometry and scratch of one decode call.  A tile holds `ht` KV heads x 128 / ht tokens; the
+// (sequence, tile) space is cut into `groups` pieces and each piece is walked by J CTAs, one per
+// (head tile, group of 8 query heads per KV head).
 struct DecodePlan {
+    int nh;                // query heads computed per KV head and item: 4 or 8
+    int ht, ht_shift;      // KV heads per tile
+    int J;                 // items
     int groups;            // pieces
-    size_t rows;           // partial-result rows: (group + sequence) * J + item
+    size_t rows;           // partial-result rows: (group + sequence) * J + item, ht * 8 slots each
     size_t prefix_bytes;
     size_t bytes;
 };
-// One 128-token tile per piece at least; at most `ctas_per_sm` CTAs per SM.  `forced` > 0 asks for that
+// The head tile: the largest of 1, 2, 4, 8 that divides the KV heads and whose query heads fit the
+// 64 accumulator columns (2 digit planes x nh query heads per KV head).  `forced` > 0 asks for that
 // many pieces per sequence.
-static DecodePlan plan_decode(int num_seqs, int H, int head_groups, int max_seq_len, int forced, int ctas_per_sm) {
-    const long long J = 1LL * H * head_groups;
-    const long long max_tiles = max_seq_len > 0 ? (max_seq_len + kTileTokens - 1) / kTileTokens : 1;
+static DecodePlan plan_decode(int num_seqs, int H, int G, int max_seq_len, int forced) {
+    DecodePlan pl;
+    pl.nh = G <= 4 ? 4 : 8;
+    pl.ht = 1;
+    pl.ht_shift = 0;
+    for (int c = 2, s = 1; c <= 8; c <<= 1, ++s)
+        if (H % c == 0 && c * 2 * pl.nh <= kMaxCols) { pl.ht = c; pl.ht_shift = s; }
+    const int head_groups = (G + kQPerHead - 1) / kQPerHead;
+    pl.J = (H / pl.ht) * head_groups;
+    const int ttok = kPairs / pl.ht;
+    const long long max_tiles = max_seq_len > 0 ? (max_seq_len + ttok - 1) / ttok : 1;
     const long long work = 1LL * num_seqs * max_tiles;
     long long groups = forced > 0 ? 1LL * forced * num_seqs : work;
-    long long cap = (forced > 0 ? 4LL : 1LL) * sm_count() * ctas_per_sm / J;
+    long long cap = (forced > 0 ? 4LL : 1LL) * sm_count() * kCtasPerSm / pl.J;
     if (cap < 1) cap = 1;
     if (groups > cap) groups = cap;
     if (groups < 1) groups = 1;
-    DecodePlan pl;
     pl.groups = static_cast<int>(groups);
-    pl.rows = static_cast<size_t>((groups + num_seqs) * J);
+    pl.rows = static_cast<size_t>((groups + num_seqs) * pl.J);
     pl.prefix_bytes = (static_cast<size_t>(num_seqs + 1) * sizeof(int32_t) + 255) / 256 * 256;
-    pl.bytes = pl.prefix_bytes + pl.rows * kHeadsPerCta * (kHeadDim + 2) * sizeof(float);
+    pl.bytes = pl.prefix_bytes + pl.rows * pl.ht * kQPerHead * (kHeadDim + 2) * sizeof(float);
     return pl;
 }
 
-// ---- tensor maps of the cache for the TMA path ------------------------------------------------
+// ---- tensor maps of the cache ------------------------------------------------------------------
 //
-// The cache is described as a 2-D byte tensor (num_slots rows of total_bytes).  cuTensorMapEncodeTiled
-// is a driver entry point; it is looked up through the runtime so that the library does not link
-// against the driver.  Maps are remembered per (cache pointer, shape, box): a serving loop calls
-// with the same cache every step.
+// The cache is described as a 2-D tensor of 8-byte elements (num_slots rows of total_bytes / 8): one
+// map per staged region, box = (region width, tokens per box), no swizzle.  cuTensorMapEncodeTiled is
+// a driver entry point; it is looked up through the runtime so that the library does not link against
+// the driver.  Maps are remembered per (cache pointer, shape, box): a serving loop calls with the same
+// cache every step.
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -1114,20 +1242,20 @@ static EncodeTiledFn encode_tiled_fn() {
 struct MapKey {
     const void* cache;
     int64_t num_slots;
-    int total_bytes, box_bytes, box_tokens, swizzle;
+    int total_bytes, box_bytes, box_rows;
     bool operator==(const MapKey& o) const {
         return cache == o.cache && num_slots == o.num_slots && total_bytes == o.total_bytes &&
-               box_bytes == o.box_bytes && box_tokens == o.box_tokens && swizzle == o.swizzle;
+               box_bytes == o.box_bytes && box_rows == o.box_rows;
     }
 };
 
 static bool encode_cache_map(CUtensorMap* map, const uint8_t* cache, int64_t num_slots, int total_bytes,
-                             int box_bytes, int box_tokens, bool swizzle64) {
+                             int box_bytes, int box_rows) {
     constexpr int kSlots = 16;
     struct Entry { MapKey key; CUtensorMap map; bool used; };
     static thread_local Entry cache_maps[kSlots] = {};
     static thread_local int next = 0;
-    const MapKey key{cache, num_slots, total_bytes, box_bytes, box_tokens, swizzle64 ? 1 : 0};
+    const MapKey key{cache, num_slots, total_bytes, box_bytes, box_rows};
     for (int i = 0; i < kSlots; ++i)
         if (cache_maps[i].used && cache_maps[i].key == key) {
             std::memcpy(map, &cache_maps[i].map, sizeof(CUtensorMap));
@@ -1135,13 +1263,13 @@ static bool encode_cache_map(CUtensorMap* map, const uint8_t* cache, int64_t num
         }
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(total_bytes), static_cast<cuuint64_t>(num_slots)};
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(total_bytes / 8), static_cast<cuuint64_t>(num_slots)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(total_bytes)};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(box_tokens)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes / 8), static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t elem[2] = {1, 1};
-    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(cache), dims, strides, box, elem,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
-           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(cache), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     Entry& e = cache_maps[next];
     next = (next + 1) % kSlots;
@@ -1152,10 +1280,10 @@ static bool encode_cache_map(CUtensorMap* map, const uint8_t* cache, int64_t num
 }
 
 // Environment switches, read once per process:
-//   RQ_DECODE_NO_TMA=1            per-row bulk copies everywhere (comparisons)
+//   RQ_DECODE_NO_TMA=1            the issuer warp copies the rows with 4-byte cp.async (the path of odd block sizes)
 //   RQ_DECODE_NO_PDL=1            launch the merge without programmatic dependent launch
 //   RQ_DECODE_EQUAL_PIECES=1      no launch-layer weights
-//   RQ_DECODE_LAYER_WEIGHTS=a,b,c weights of the launch layers (defaults below)
+//   RQ_DECODE_LAYER_WEIGHTS=a,b   weights of the launch layers (defaults below)
 struct DecodeEnv {
     bool no_tma, no_pdl, equal_pieces;
     int weights[kMaxLayers];
@@ -1184,36 +1312,60 @@ static const DecodeEnv& decode_env() {
     return env;
 }
 
-template <typename T, int KB, int VB, int MODE>
-static int launch_attn(const DecodeParams& p, const CUtensorMap& map_k, const CUtensorMap& map_v, cudaStream_t st) {
-    const size_t smem = sizeof(DecodeSmem<MODE>) + 1024;                     // + hand alignment
-    const long long ctas = 1LL * p.groups * p.H * p.head_groups;
-    auto launch = [&](auto kernel) -> int {
-        if (int e = ensure_smem(kernel, smem)) return e;
-        kernel<<<static_cast<unsigned>(ctas), kDecodeThreads, smem, st>>>(p, map_k, map_v);
-        return check_cuda(cudaGetLastError(), "rq_decode attention launch");
-    };
-    return p.G <= 4 ? launch(decode_attn_kernel<T, KB, VB, MODE, 4>) : launch(decode_attn_kernel<T, KB, VB, MODE, 8>);
+// Staging layout of a stage for this geometry: one region when the head tile is the whole slot payload,
+// else the four regions, each widened to 16-byte boundaries.
+static void plan_staging(DecodeParams& p) {
+    const int ttok = p.ttok;
+    if (p.ht == p.H) {
+        p.n_regions = 1;
+        p.reg_w[0] = (136 * p.H + 15) / 16 * 16;
+        p.reg_base[0] = 0;
+        for (int r = 1; r < kRegions; ++r) { p.reg_w[r] = 0; p.reg_base[r] = 0; }
+        p.stage_bytes = ttok * p.reg_w[0];
+    } else {
+        p.n_regions = kRegions;
+        int base = 0;
+        for (int r = 0; r < kRegions; ++r) {
+            const int len = ((r & 1) ? 4 : kHalfDim) * p.ht;
+            int off_max = 0;
+            for (int h0 = 0; h0 < p.H; h0 += p.ht) {
+                const RegionWindow rw = region_window(p.H, h0);
+                off_max = std::max(off_max, rw.start[r] - rw.x[r]);
+            }
+            p.reg_w[r] = (off_max + len + 15) / 16 * 16;
+            p.reg_base[r] = base;
+            base += ttok * p.reg_w[r];
+        }
+        p.stage_bytes = base;
+    }
+    p.stages = std::min(kMaxStages, kRingBytes / p.stage_bytes);
+    p.v_aligned = p.H % 4 == 0 ? 1 : 0;
 }
 
 template <typename T, int KB, int VB>
-static int launch_decode(DecodeParams& p, int mode, cudaStream_t st) {
+static int launch_decode(DecodeParams& p, int nh, cudaStream_t st) {
     if (!p.inline_plan) {
-        decode_plan_kernel<<<1, 1024, 0, st>>>(p.seq_lens, p.num_seqs, p.prefix);
+        decode_plan_kernel<<<1, 1024, 0, st>>>(p.seq_lens, p.num_seqs, p.ttok, p.prefix);
         if (int e = check_cuda(cudaGetLastError(), "rq_decode plan launch")) return e;
     }
-    alignas(64) CUtensorMap map_k{}, map_v{};
+    alignas(64) TmaMaps maps{};
     const int64_t num_slots = p.num_blocks * p.block_size;
-    if (mode != 0) {
-        const bool ok = encode_cache_map(&map_k, p.cache, num_slots, p.total_bytes, kHalfDim, p.box_tokens, true) &&
-                        encode_cache_map(&map_v, p.cache, num_slots, p.total_bytes, mode == 1 ? kHalfDim : 80,
-                                         p.box_tokens, mode == 1);
-        if (!ok) mode = 0;                                                 // no tensor maps: per-row copies
+    if (p.box_rows > 0) {
+        bool ok = true;
+        for (int r = 0; r < p.n_regions && ok; ++r)
+            ok = encode_cache_map(&maps.m[r], p.cache, num_slots, p.total_bytes, p.reg_w[r], p.box_rows);
+        if (!ok) p.box_rows = 0;                                           // no tensor maps: word copies
     }
-    int e = mode == 1   ? launch_attn<T, KB, VB, 1>(p, map_k, map_v, st)
-            : mode == 2 ? launch_attn<T, KB, VB, 2>(p, map_k, map_v, st)
-                        : launch_attn<T, KB, VB, 0>(p, map_k, map_v, st);
-    if (e) return e;
+    {
+        const size_t smem = sizeof(DecodeSmem) + 1024;                       // + hand alignment
+        const long long ctas = 1LL * p.groups * (p.H >> p.ht_shift) * p.head_groups;
+        auto launch = [&](auto kernel) -> int {
+            if (int e = ensure_smem(kernel, smem)) return e;
+            kernel<<<static_cast<unsigned>(ctas), kDecodeThreads, smem, st>>>(p, maps);
+            return check_cuda(cudaGetLastError(), "rq_decode attention launch");
+        };
+        if (int e = nh == 4 ? launch(decode_attn_kernel<T, KB, VB, 4>) : launch(decode_attn_kernel<T, KB, VB, 8>)) return e;
+    }
 
     const long long warps = 1LL * p.num_seqs * p.Hq;
     const unsigned grid = static_cast<unsigned>((warps + kMergeWarps - 1) / kMergeWarps);
@@ -1235,17 +1387,11 @@ static int launch_decode(DecodeParams& p, int mode, cudaStream_t st) {
 }
 
 template <typename T>
-static int dispatch_bits(DecodeParams& p, int mode, int kb, int vb, cudaStream_t st) {
-    if (kb == 3 && vb == 3) return launch_decode<T, 3, 3>(p, mode, st);
-    if (kb == 4 && vb == 3) return launch_decode<T, 4, 3>(p, mode, st);
-    if (kb == 3 && vb == 4) return launch_decode<T, 3, 4>(p, mode, st);
-    return launch_decode<T, 4, 4>(p, mode, st);
-}
-
-// How the rows of a tile are staged for this cache geometry (see DecodeSmem).
-static int staging_mode(int num_kv_heads, int block_size, int bs_shift, const uint8_t* cache, int64_t num_blocks) {
-    if (decode_env().no_tma || bs_shift < 3 || !aligned(cache, 16) || num_blocks * block_size > INT32_MAX) return 0;
-    return num_kv_heads % 4 == 0 ? 1 : 2;
+static int dispatch_bits(DecodeParams& p, int nh, int kb, int vb, cudaStream_t st) {
+    if (kb == 3 && vb == 3) return launch_decode<T, 3, 3>(p, nh, st);
+    if (kb == 4 && vb == 3) return launch_decode<T, 4, 3>(p, nh, st);
+    if (kb == 3 && vb == 4) return launch_decode<T, 3, 4>(p, nh, st);
+    return launch_decode<T, 4, 4>(p, nh, st);
 }
 
 }  // namespace rq
@@ -1256,10 +1402,7 @@ extern "C" size_t rq_decode_workspace_bytes(int num_seqs, int num_q_heads, int n
                                             int head_dim, int max_seq_len, int num_splits) {
     if (num_seqs <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim != kHeadDim) return 0;
     if (num_q_heads % num_kv_heads != 0) return 0;
-    const int G = num_q_heads / num_kv_heads;
-    const int head_groups = (G + kHeadsPerCta - 1) / kHeadsPerCta;
-    // sized for the densest launch (three CTAs per SM) whatever staging mode the call will use
-    return plan_decode(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits, kMaxCtasPerSm).bytes;
+    return plan_decode(num_seqs, num_kv_heads, num_q_heads / num_kv_heads, max_seq_len, num_splits).bytes;
 }
 
 extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq,
@@ -1297,21 +1440,19 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
         return fail(RQ_ERR_ALIGNMENT, "rq_decode: kv_cache and rotation must be 16-byte aligned");
 
     const int G = num_q_heads / num_kv_heads;
-    const int head_groups = (G + kHeadsPerCta - 1) / kHeadsPerCta;
-    if (static_cast<long long>(num_kv_heads) * head_groups > 65535)
+    const int head_groups = (G + kQPerHead - 1) / kQPerHead;
+    const DecodePlan pl = plan_decode(num_seqs, num_kv_heads, G, max_seq_len, num_splits);
+    if (static_cast<long long>(pl.J) > 65535)
         return fail(RQ_ERR_UNSUPPORTED, "rq_decode: too many KV heads");
-    int bs_shift = -1;
-    for (int sft = 0; sft < 31; ++sft)
-        if ((1 << sft) == block_size) bs_shift = sft;
-    const int mode = staging_mode(num_kv_heads, block_size, bs_shift, kv_cache, num_blocks);
-    const int ctas_per_sm = mode == 1 ? DecodeSmem<1>::kCtasPerSm : DecodeSmem<2>::kCtasPerSm;
-    const DecodePlan pl = plan_decode(num_seqs, num_kv_heads, head_groups, max_seq_len, num_splits, ctas_per_sm);
     const size_t need = pl.bytes;
     if (!workspace || workspace_bytes < need)
         return fail(RQ_ERR_WORKSPACE, "rq_decode: workspace of %zu bytes needed, %zu given", need,
                     workspace_bytes);
     if (!aligned(workspace, 16))
         return fail(RQ_ERR_ALIGNMENT, "rq_decode: workspace must be 16-byte aligned");
+    int bs_shift = -1;
+    for (int sft = 0; sft < 31; ++sft)
+        if ((1 << sft) == block_size) bs_shift = sft;
 
     DecodeParams p{};
     p.q = q; p.q_stride_seq = q_stride_seq; p.q_stride_head = q_stride_head;
@@ -1320,37 +1461,50 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
     p.seq_lens = seq_lens; p.cent_k = centroids_k; p.cent_v = centroids_v; p.rotation = rotation;
     p.qk_scale = sm_scale * 1.4426950408889634f;
     p.H = num_kv_heads; p.Hq = num_q_heads; p.G = G; p.head_groups = head_groups;
+    p.ht = pl.ht; p.ht_shift = pl.ht_shift;
+    p.ttok = kPairs / pl.ht;
+    p.ttok_shift = 7 - pl.ht_shift;
+    p.n_cols = std::max(16, pl.ht * 2 * pl.nh);
     p.prefix = static_cast<int32_t*>(workspace);
-    const size_t rows = pl.rows * kHeadsPerCta;
+    const size_t slots = pl.rows * pl.ht * kQPerHead;
     p.ws_o = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.prefix_bytes);
-    p.ws_m = p.ws_o + rows * kHeadDim;
-    p.ws_l = p.ws_m + rows;
+    p.ws_m = p.ws_o + slots * kHeadDim;
+    p.ws_l = p.ws_m + slots;
     p.num_seqs = num_seqs; p.groups = pl.groups;
     p.inline_plan = num_seqs <= kInlinePlanSeqs ? 1 : 0;
     p.bs_shift = bs_shift;
-    p.box_tokens = block_size >= 16 ? 16 : block_size;
-    // Launch-layer weights: only when (nearly) every SM holds its full set of CTAs.  The defaults were
-    // fitted on a B200 from the finish times of equal pieces (see weight_cum); RQ_DECODE_LAYER_WEIGHTS
-    // overrides them.
+    plan_staging(p);
+    // TMA boxes: power-of-two blocks of 8 tokens or more, slot numbers that fit a 32-bit coordinate
     const DecodeEnv& env = decode_env();
+    p.box_rows = (!env.no_tma && bs_shift >= 3 && num_blocks * block_size <= INT32_MAX) ? std::min(block_size, p.ttok) : 0;
+    // Launch-layer weights: only when (nearly) every SM holds its full set of CTAs.  RQ_DECODE_LAYER_WEIGHTS
+    // overrides the defaults.
     const int sms = sm_count();
-    const long long ctas = 1LL * pl.groups * num_kv_heads * head_groups;
+    const long long ctas = 1LL * pl.groups * pl.J;
     p.layer_ctas = 0;
-    p.num_layers = ctas_per_sm;
-    static const int kDefault3[kMaxLayers] = {1024, 1024, 1024, 1024};
-    static const int kDefault2[kMaxLayers] = {1024, 1024, 1024, 1024};
-    for (int i = 0; i < kMaxLayers; ++i) {
-        const int* def = ctas_per_sm == 3 ? kDefault3 : kDefault2;
-        p.layer_w[i] = env.n_weights > 0 ? env.weights[i < env.n_weights ? i : env.n_weights - 1] : def[i];
-    }
-    if (!env.equal_pieces && ctas > 1LL * (ctas_per_sm - 1) * sms) p.layer_ctas = sms;
+    p.num_layers = kCtasPerSm;
+    static const int kDefaultWeights[kMaxLayers] = {1024, 1024, 1024, 1024};
+    for (int i = 0; i < kMaxLayers; ++i)
+        p.layer_w[i] = env.n_weights > 0 ? env.weights[i < env.n_weights ? i : env.n_weights - 1] : kDefaultWeights[i];
+    if (!env.equal_pieces && ctas > 1LL * (kCtasPerSm - 1) * sms) p.layer_ctas = sms;
     p.out = out; p.o_stride_seq = o_stride_seq; p.o_stride_head = o_stride_head;
+#ifdef RQ_DECODE_TRACE
+    p.trace = g_trace_buffer;
+#endif
 
     const int kb = n_centroids_k == 8 ? 3 : 4, vb = n_centroids_v == 8 ? 3 : 4;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == RQ_DTYPE_BF16) return dispatch_bits<__nv_bfloat16>(p, mode, kb, vb, st);
-    return dispatch_bits<__half>(p, mode, kb, vb, st);
+    if (dtype == RQ_DTYPE_BF16) return dispatch_bits<__nv_bfloat16>(p, pl.nh, kb, vb, st);
+    return dispatch_bits<__half>(p, pl.nh, kb, vb, st);
 }
+
+#ifdef RQ_DECODE_TRACE
+// Development builds only: device buffer of 3 x 5 x 64 x 16 clock values (see RQ_TRACE).
+extern "C" int rq_debug_set_trace(void* device_buffer) {
+    rq::g_trace_buffer = static_cast<unsigned long long*>(device_buffer);
+    return RQ_OK;
+}
+#endif
 
 // ---- decode with library-owned scratch ------------------------------------------------------
 //

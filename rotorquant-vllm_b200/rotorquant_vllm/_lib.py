@@ -12,7 +12,8 @@ import os
 
 import torch
 
-_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "librq_b200.so")
+# RQ_B200_LIBRARY: path of another build of the library (A/B comparisons of kernel variants).
+_PATH = os.environ.get("RQ_B200_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "librq_b200.so")
 _LIB = None
 
 RQ_OK = 0

@@ -77,7 +77,7 @@ def test_bad_arguments_are_rejected_without_a_device():
     assert L.rq_probe_mma_peak(2, 16, None, None, None) == _lib.RQ_ERR_INVALID_ARG
     # zero work is fine
     assert L.rq_compress(None, 2, 0, 128, 128, None, None, 7, None, None, None) == 0
-    # forced: one piece per sequence -> 4 groups of 8 warps; rows = (groups + sequences) * 8 items, 8 heads each
+    # forced: one piece per sequence -> 4 groups; rows = groups + sequences (one item), 8 KV heads x 8 slots each
     assert L.rq_decode_workspace_bytes(4, 32, 8, 128, 2048, 1) == 256 + (4 + 4) * 8 * 8 * 130 * 4
 
 

@@ -196,9 +196,10 @@ def test_bytes_past_the_end_of_a_sequence_are_ignored(dtype):
 
 
 def test_row_copy_staging_in_a_subprocess():
-    """RQ_DECODE_NO_TMA=1 (read once per process) stages the index rows with one bulk copy per
-    token instead of TMA boxes, the path every unusual block size takes: run the golden and edge
-    cases under it in a child process."""
+    """RQ_DECODE_NO_TMA=1 (read once per process) stages the rows with 4-byte copies issued by the
+    issuer warp instead of TMA boxes, the path every unusual block size takes; RQ_DECODE_NO_PDL=1
+    launches the merge without programmatic dependent launch and RQ_DECODE_EQUAL_PIECES=1 cuts the
+    tile line into equal pieces.  Run the golden and edge cases under them in a child process."""
     import os
     import subprocess
     import sys
@@ -206,7 +207,7 @@ def test_row_copy_staging_in_a_subprocess():
     if os.environ.get("RQ_DECODE_NO_TMA"):
         pytest.skip("already running with row copies")
     here = os.path.dirname(os.path.abspath(__file__))
-    env = dict(os.environ, RQ_DECODE_NO_TMA="1")
+    env = dict(os.environ, RQ_DECODE_NO_TMA="1", RQ_DECODE_NO_PDL="1", RQ_DECODE_EQUAL_PIECES="1")
     res = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_decode_gpu.py"), "-x", "-q",
                           "-m", "gpu", "-k", "golden or past_the_end or fresh or growing"],
                          env=env, capture_output=True, text=True, timeout=900)

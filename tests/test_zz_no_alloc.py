@@ -21,7 +21,7 @@ from rotorquant_vllm import synthetic as syn
 
 pytestmark = pytest.mark.gpu
 
-STATIC_BYTES = 4 << 20
+STATIC_BYTES = 16 << 20
 
 
 def _case(lens, seed):
