@@ -125,6 +125,16 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 // Wait until the phase with the given parity has completed.  Every wait in this library is
 // bounded (about one second of SM clocks); false means the bound expired.
+// One non-blocking look: has the phase with the given parity completed?
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
 constexpr long long kWaitCycles = 2000000000LL;
 __device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, long long limit_cycles) {
     const uint32_t addr = smem_u32(bar);

@@ -17,11 +17,15 @@
 // leaves one partial result per sequence its piece touches.  A second launch merges the partial
 // results of every (sequence, query head), rounds, and applies R.
 //
-// The attention CTA is warp specialised: four compute warps (thread t owns pair t of the tile and
-// TMEM lane t) and one issuer warp that owns every asynchronous engine -- it fills a ring of staged
-// tiles with TMA boxes and issues the tcgen05 MMAs when the compute warps have published their
-// operands.  Compute warps never issue a copy or an MMA and meet no block-wide barrier inside the
-// tile loop; everything is ordered by mbarriers.
+// The attention CTA is warp specialised.  Two threads work on every pair: thread t of the four K
+// warps (which owns TMEM lane t) builds the pair's K digit planes, reads its scores and runs the
+// softmax; thread t of the four V warps decompresses the pair's V row into the shared V tile at the
+// same time.  Two more warps own the asynchronous engines.  Issuing a tcgen05.mma of these skinny
+// shapes keeps the issuing thread busy for 100 (S^T, N = 64) to 140 cycles (O^T) whatever else runs, and
+// two threads of different warps issue side by side without slowing each other, so one warp issues the
+// S^T MMAs and fills the ring of staged tiles with TMA boxes, the other issues the O^T MMAs, each when the
+// other warps have published its operands.  No block-wide barrier is met inside the tile loop;
+// everything is ordered by mbarriers.
 //
 // Arithmetic (matches "reference decompress + SDPA"):
 //   q_rot   = round_T(q @ R^T)            exact FMA chain per 4x4 block, computed per part
@@ -53,8 +57,10 @@ namespace rq {
 constexpr int kQPerHead = 8;                 // query-head slots per KV head of a partial row / of one item
 constexpr int kPairs = 128;                  // (token, KV head) pairs per tile = compute threads per CTA
 constexpr int kComputeThreads = 128;
-constexpr int kDecodeThreads = 160;          // + the issuer warp
-constexpr int kIssuerWarp = 4;
+constexpr int kDecodeThreads = 320;          // K warps 0..3, V warps 4..7, two issuer warps
+constexpr int kVWarp0 = 4;
+constexpr int kSIssuerWarp = 8;              // issues S^T = K Q^T and the TMA copies
+constexpr int kPvIssuerWarp = 9;             // issues O^T += V^T P
 constexpr uint32_t kTmemCols = 256;          // columns allocated per CTA
 constexpr uint32_t kColKhi = 0, kColKlo = 32, kColS = 64, kColS2 = 128, kColO = 192;
 constexpr int kMaxCols = 64;                 // columns of one S accumulator and of O: head tile x 2 x query heads
@@ -343,16 +349,17 @@ struct DecodeSmem {
     alignas(128) uint16_t v[kPairs * kHeadDim];        // V tile: core (pair/8)*16 + pos/8, core row pair%8
     uint16_t p[kPairs * 16];                           // P tile: core (pair/8)*2 + n/8, core row pair%8
     uint8_t q[kMaxCols * kHeadDim];                    // Q digit planes, K-major: core (n/8)*8 + pos/16
-    float cb[2][16];
+    alignas(16) float cb[2][16];
     float qf[32];                                      // per (head of the tile, query head): q unscale * sm_scale * log2(e)
     float mref[32];                                    // reference maxima, kept by the first lane of every head
     float alpha[32];                                   // rescale factors of a moved reference
     float red_m[8][kQPerHead];                         // per half warp (16 pairs of one head)
     float red_l[8][kQPerHead];
     int scan[4];
-    uint64_t full[kMaxStages];                         // "the tile's rows landed"
-    uint64_t kready, pvready;                          // compute -> issuer: operands published (128 arrivals)
-    uint64_t bar_s, bar_o, bar_drain;                  // issuer -> compute: MMAs complete
+    uint64_t full[kMaxStages];                         // copy warp -> K / V warps: "the tile's rows landed"
+    uint64_t empty[kMaxStages];                        // K / V warps -> copy warp: rows read (8 arrivals: one per warp)
+    uint64_t kready, pvready, vready;                  // K / V warps -> issuer: operands published (128 arrivals each)
+    uint64_t bar_s, bar_o, bar_vfree, bar_drain, bar_drain2;   // issuers -> K / V warps: MMAs complete
     uint32_t tmem_base;
     int grow_tile, redo_tile, dead;
     int32_t prefix[kInlinePlanSeqs + 1];
@@ -395,12 +402,18 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
 
     // ---- set-up: barriers, tensor memory, codebooks, tile prefix sums, a zero P tile ----
     if (tid == 0) {
-        for (int s = 0; s < kMaxStages; ++s) mbar_init(&sm.full[s], p.box_rows > 0 ? 1 : 32);
+        for (int s = 0; s < kMaxStages; ++s) {
+            mbar_init(&sm.full[s], p.box_rows > 0 ? 1 : 32);
+            mbar_init(&sm.empty[s], 8);
+        }
         mbar_init(&sm.kready, kComputeThreads);
         mbar_init(&sm.pvready, kComputeThreads);
+        mbar_init(&sm.vready, kComputeThreads);
         mbar_init(&sm.bar_s, 1);
         mbar_init(&sm.bar_o, 1);
+        mbar_init(&sm.bar_vfree, 1);
         mbar_init(&sm.bar_drain, 1);
+        mbar_init(&sm.bar_drain2, 1);
         sm.grow_tile = -1;
         sm.redo_tile = -1;
         sm.dead = 0;
@@ -411,7 +424,7 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
         reinterpret_cast<uint4*>(sm.p)[i] = make_uint4(0u, 0u, 0u, 0u);
     fence_async_proxy();
     if (warp == 0) tmem_alloc(&sm.tmem_base, kTmemCols);
-    if (warp == kIssuerWarp) {
+    if (warp == kSIssuerWarp) {
         const int kv = lane >> 4, i = lane & 15;
         const int n = kv ? NV : NK;
         sm.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
@@ -489,17 +502,15 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
 #ifdef RQ_DECODE_TRACE
     // CTAs 0, 100 and 200: [cta][warp][tile][16 points]
     unsigned long long* trace_row = nullptr;
-    if (p.trace != nullptr && blockIdx.x % 100 == 0 && blockIdx.x / 100 < 3)
-        trace_row = p.trace + ((blockIdx.x / 100) * 5 + warp) * 64 * 16;
+    if (p.trace != nullptr && blockIdx.x % 100 == 0 && blockIdx.x / 100 < 3 && (warp < kVWarp0 || warp == kSIssuerWarp))
+        trace_row = p.trace + ((blockIdx.x / 100) * 5 + (warp == kSIssuerWarp ? 4 : warp)) * 64 * 16;
 #endif
 
-    if (has_work && warp == kIssuerWarp) {
-        // =========================== issuer warp ===========================
+    if (has_work && warp == kSIssuerWarp) {
+        // ============ S issuer + copy warp: S^T = K Q^T of every tile, and the rows of the tiles ahead ============
         const uint32_t ncols = static_cast<uint32_t>(p.n_cols);
         const uint32_t idesc_s = (2u << 4) | (1u << 7) | (1u << 10) | ((ncols >> 3) << 17) | ((128u >> 4) << 24);
-        const uint32_t idesc_o = (1u << 4) | (TcFormat<T>::kFmt << 7) | (TcFormat<T>::kFmt << 10) | (1u << 15) |
-                                 (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-        const uint32_t q_addr = smem_u32(sm.q), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p);
+        const uint32_t q_addr = smem_u32(sm.q);
         const uint32_t ring_addr = smem_u32(sm.ring);
 
         // ---- producer: the rows of one tile into ring stage (n % S) ----
@@ -564,19 +575,31 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
             if (advance(pw)) p_seq_len = max(__ldg(p.seq_lens + pw.seq), 0);
             prefetch_blk();
         };
-#pragma unroll 1
-        for (int s = 0; s < S && pw.x < x_end; ++s) produce();
+        // Tile n >= S may be copied once the K and the V warps have read the rows of tile n - S out of its
+        // stage.  Tiles the next iteration cannot do without are waited for; further ahead, a stage that
+        // is not free yet is simply tried again later.
+        auto produce_ahead = [&](int it_now) {
+            while (pw.x < x_end && !dead) {
+                const int n = produced;
+                if (n >= S) {
+                    const uint32_t parity = ((n / S) - 1) & 1;
+                    if (n <= it_now + 1) {
+                        if (!mbar_wait(&sm.empty[n % S], parity)) { dead = true; return; }
+                    } else if (!mbar_test(&sm.empty[n % S], parity)) {
+                        return;
+                    }
+                }
+                produce();
+            }
+        };
+        produce_ahead(-1);
 
-        // ---- consumer of the compute warps' operands: issue the MMAs of every tile ----
         Walk cw;
         start_walk(cw);
-        bool first_in_part = true;
-        uint32_t ph_pv = 0;
         int it = 0;
-        const int cols_per_head = 2 * NH;
 #pragma unroll 1
-        for (; cw.x < x_end; ++it) {
-            // S^T = K Q^T: the digit planes of the tile are in tensor memory, the query planes in shared memory
+        for (; cw.x < x_end && !dead; ++it) {
+            // the digit planes of the tile are in tensor memory, the query planes in shared memory
             RQ_TRACE(0);
             if (!mbar_wait(&sm.kready, it & 1)) { dead = true; break; }
             RQ_TRACE(1);
@@ -594,12 +617,37 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
             }
             __syncwarp();
             RQ_TRACE(2);
-            // O^T += V^T [P hi | P lo], one k-step of 16 pairs (one KV head) at a time
+            produce_ahead(it);
+            RQ_TRACE(5);
+            advance(cw);
+        }
+        if (dead) {
+            st_volatile_shared(&sm.dead, 1);
+            // copies still in flight: a bounded wait each, so that none lands after the CTA is gone
+            if (p.box_rows > 0)
+                for (int c = max(0, produced - S); c < produced; ++c) mbar_wait(&sm.full[c % S], (c / S) & 1);
+            if (lane == 0) tc_commit(&sm.bar_drain);
+            __syncwarp();
+            mbar_wait(&sm.bar_drain, 0);
+        }
+        cp_async_wait_all();
+    } else if (has_work && warp == kPvIssuerWarp) {
+        // ============ P V issuer: O^T += V^T [P hi | P lo], one k-step of 16 pairs (one KV head) at a time ============
+        const uint32_t idesc_o = (1u << 4) | (TcFormat<T>::kFmt << 7) | (TcFormat<T>::kFmt << 10) | (1u << 15) |
+                                 (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+        const uint32_t v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p);
+        Walk cw;
+        start_walk(cw);
+        bool first_in_part = true;
+        uint32_t ph_pv = 0;
+        int it = 0;
+        const int cols_per_head = 2 * NH;
+#pragma unroll 1
+        for (; cw.x < x_end; ++it) {
             if (!mbar_wait(&sm.pvready, ph_pv)) { dead = true; break; }
-            RQ_TRACE(3);
             ph_pv ^= 1u;
             if (ld_volatile_shared(&sm.grow_tile) == it) {
-                // a score outgrew the reference maximum: hand the tile back; the compute warps move the
+                // a score outgrew the reference maximum: hand the tile back; the K warps move the
                 // maxima, rescale, rewrite P and publish again
                 if (lane == 0) {
                     st_volatile_shared(&sm.redo_tile, it);
@@ -609,6 +657,7 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
                 if (!mbar_wait(&sm.pvready, ph_pv)) { dead = true; break; }
                 ph_pv ^= 1u;
             }
+            if (!mbar_wait(&sm.vready, it & 1)) { dead = true; break; }
             tc_fence_after();
             if (lane == 0) {
                 int prev_blk = -1;
@@ -622,28 +671,20 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
                                smem_desc(p_addr + 512 * s, 256, 128), idesc_o, acc);
                 }
                 tc_commit(&sm.bar_o);
+                tc_commit(&sm.bar_vfree);
             }
             __syncwarp();
-            RQ_TRACE(4);
-            // every compute thread has read its rows of this tile's stage: refill it
-            if (pw.x < x_end) produce();
-            RQ_TRACE(5);
             first_in_part = advance(cw);
         }
         if (dead) {
             st_volatile_shared(&sm.dead, 1);
-            // copies still in flight: a bounded wait each, so that none lands after the CTA is gone
-            if (p.box_rows > 0)
-                for (int c = it; c < produced; ++c) mbar_wait(&sm.full[c % S], (c / S) & 1);
-            if (lane == 0) tc_commit(&sm.bar_drain);
+            if (lane == 0) tc_commit(&sm.bar_drain2);
             __syncwarp();
-            mbar_wait(&sm.bar_drain, 0);
+            mbar_wait(&sm.bar_drain2, 0);
         }
-        cp_async_wait_all();
-    } else if (has_work) {
-        // =========================== compute warps ===========================
+    } else if (has_work && warp < kVWarp0) {
+        // =========================== K warps: digit planes, scores, softmax ===========================
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lane quarter
-        uint8_t* const v_dst = reinterpret_cast<uint8_t*>(sm.v) + (tid >> 3) * (16 * 128) + (tid & 7) * 16;
         const int hh = tid >> p.ttok_shift, tt = tid & (p.ttok - 1);      // this pair: KV head of the tile, token
         const int half = tid >> 4;                                         // 16 pairs of one head
         const int halves_per_head = p.ttok >> 4, first_half = (half / halves_per_head) * halves_per_head;
@@ -665,6 +706,8 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
 
         uint32_t ph_o = 0;
         int it = 0;                                // tiles streamed by this CTA so far
+        int stage = 0;                             // it % S, and the parity of that stage's "landed" barrier
+        uint32_t ph_full = 0;
         int64_t x = x0;
         int seq = find_seq(prefix, p.num_seqs, x0);
 
@@ -812,11 +855,12 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
 
 #pragma unroll 1
             for (int tile = t_begin; tile < t_end; ++tile, ++it) {
-                const int stage = it % S;
                 const bool valid = (tile << p.ttok_shift) + tt < seq_len;
                 const uint8_t* stg = sm.ring + stage * p.stage_bytes;
+                const int this_stage = stage;
                 RQ_TRACE(0);
-                if (!mbar_wait(&sm.full[stage], (it / S) & 1)) { dead = true; break; }
+                if (!mbar_wait(&sm.full[stage], ph_full)) { dead = true; break; }
+                if (++stage == S) { stage = 0; ph_full ^= 1u; }
                 RQ_TRACE(1);
 
                 // ---- K table, digit planes -> tensor memory ----
@@ -824,7 +868,13 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
                 {
                     // a zero norm makes every table entry zero: pairs past the end contribute nothing
                     const float nk = valid ? *reinterpret_cast<const float*>(stg + f_off[1]) : 0.0f;
-                    const Table<KB> tk = build_int_table<T, KB>(sm.cb[0], cmax_k, nk, k_unscale);
+                    float cbk[NK];
+#pragma unroll
+                    for (int i = 0; i < NK; i += 4) {
+                        const float4 c4 = *reinterpret_cast<const float4*>(&sm.cb[0][i]);
+                        cbk[i] = c4.x; cbk[i + 1] = c4.y; cbk[i + 2] = c4.z; cbk[i + 3] = c4.w;
+                    }
+                    const Table<KB> tk = build_int_table<T, KB>(cbk, cmax_k, nk, k_unscale);
                     const uint8_t* krow = stg + f_off[0];
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf) {
@@ -842,61 +892,26 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
                     }
                 }
                 RQ_TRACE(2);
+                __syncwarp();                        // every lane holds its K row and norm in registers:
+                if (lane == 0) mbar_arrive(&sm.empty[this_stage]);   // this warp is done with the stage
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&sm.kready);
                 RQ_TRACE(3);
 
-                // ---- V row -> shared tile (the previous tile's P V must have read it) ----
+                // ---- the previous tile's P V must be complete before P is rewritten (and may hand the tile back) ----
                 if (pending) {
                     settle_pending();
                     if (dead) break;
                 }
                 RQ_TRACE(4);
                 uint32_t d1[16], d2[16];                     // this pair's sums: 16 columns of each accumulator
-                {
-                    Table<VB> tb = build_value_table<T, VB>(sm.cb[1], *reinterpret_cast<const float*>(stg + f_off[3]));
-                    if (!valid) {
-                        // rows past the end of the sequence may hold bytes that are not index nibbles; with an
-                        // all-zero table every PRMT result is zero whatever the selector (a -0.0 entry would
-                        // turn a selector with its top bit set into a sign mask, i.e. a NaN pattern in fp16)
-#pragma unroll
-                        for (int r = 0; r < Table<VB>::kRegs; ++r) tb.r[r] = 0u;
-                    }
-                    const uint8_t* vrow = stg + f_off[2];
-#pragma unroll
-                    for (int quarter = 0; quarter < 4; ++quarter) {
-                        if (quarter == 2) {
-                            // S^T is normally complete by now: request this pair's sums so that the
-                            // tensor-memory read runs under the second half of the V row
-                            RQ_TRACE(5);
-                            if (!mbar_wait(&sm.bar_s, it & 1)) { dead = true; break; }
-                            RQ_TRACE(6);
-                            tc_fence_after();
-                            tmem_ld16_nowait(lane_base + kColS + col16, d1);
-                            tmem_ld16_nowait(lane_base + kColS2 + col16, d2);
-                        }
-                        uint32_t words[4];
-                        if (p.v_aligned) {
-                            const uint4 w4 = *reinterpret_cast<const uint4*>(vrow + 16 * quarter);
-                            words[0] = w4.x; words[1] = w4.y; words[2] = w4.z; words[3] = w4.w;
-                        } else {
-#pragma unroll
-                            for (int w = 0; w < 4; ++w)
-                                words[w] = *reinterpret_cast<const uint32_t*>(vrow + 16 * quarter + 4 * w);
-                        }
-#pragma unroll
-                        for (int w = 0; w < 4; ++w) {          // 8 head-dims = one 32-bit index word per chunk
-                            uint32_t lo0, hi0, lo1, hi1;
-                            lookup4<VB>(tb, words[w], lo0, hi0);
-                            lookup4<VB>(tb, words[w] >> 16, lo1, hi1);
-                            *reinterpret_cast<uint4*>(v_dst + (4 * quarter + w) * 128) =
-                                make_uint4(prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
-                                           prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
-                        }
-                    }
-                    if (dead) break;
-                }
+                RQ_TRACE(5);
+                if (!mbar_wait(&sm.bar_s, it & 1)) { dead = true; break; }
+                RQ_TRACE(6);
+                tc_fence_after();
+                tmem_ld16_nowait(lane_base + kColS + col16, d1);
+                tmem_ld16_nowait(lane_base + kColS2 + col16, d2);
 
                 // ---- scores, reference maxima, probabilities ----
                 const float tok_bias = valid ? 0.0f : -INFINITY;
@@ -994,6 +1009,72 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
 
             x += t_end - t_begin;
             if (t_end == n_s) ++seq;
+        }
+        if (dead) st_volatile_shared(&sm.dead, 1);
+    } else if (has_work) {
+        // =========================== V warps: V rows -> shared V tile ===========================
+        const int pair = tid - 32 * kVWarp0;
+        uint8_t* const v_dst = reinterpret_cast<uint8_t*>(sm.v) + (pair >> 3) * (16 * 128) + (pair & 7) * 16;
+        const int hh = pair >> p.ttok_shift, tt = pair & (p.ttok - 1);
+        const int unit_v = kHalfDim;
+        const int v_off = p.n_regions == 1 ? tt * p.reg_w[0] + rw.start[2] + unit_v * hh
+                                           : p.reg_base[2] + tt * p.reg_w[2] + (rw.start[2] - rw.x[2]) + unit_v * hh;
+        const int vn_off = p.n_regions == 1 ? tt * p.reg_w[0] + rw.start[3] + 4 * hh
+                                            : p.reg_base[3] + tt * p.reg_w[3] + (rw.start[3] - rw.x[3]) + 4 * hh;
+        Walk vw;
+        start_walk(vw);
+        int seq_len = max(__ldg(p.seq_lens + vw.seq), 0);
+        int stage = 0;
+        uint32_t ph_full = 0;
+#pragma unroll 1
+        for (int it = 0; vw.x < x_end; ++it) {
+            const bool valid = (vw.tile << p.ttok_shift) + tt < seq_len;
+            const uint8_t* stg = sm.ring + stage * p.stage_bytes;
+            const int this_stage = stage;
+            if (!mbar_wait(&sm.full[stage], ph_full)) { dead = true; break; }
+            if (++stage == S) { stage = 0; ph_full ^= 1u; }
+            float cbv[NV];
+#pragma unroll
+            for (int i = 0; i < NV; i += 4) {
+                const float4 c4 = *reinterpret_cast<const float4*>(&sm.cb[1][i]);
+                cbv[i] = c4.x; cbv[i + 1] = c4.y; cbv[i + 2] = c4.z; cbv[i + 3] = c4.w;
+            }
+            Table<VB> tb = build_value_table<T, VB>(cbv, *reinterpret_cast<const float*>(stg + vn_off));
+            if (!valid) {
+                // rows past the end of the sequence may hold bytes that are not index nibbles; with an
+                // all-zero table every PRMT result is zero whatever the selector (a -0.0 entry would
+                // turn a selector with its top bit set into a sign mask, i.e. a NaN pattern in fp16)
+#pragma unroll
+                for (int r = 0; r < Table<VB>::kRegs; ++r) tb.r[r] = 0u;
+            }
+            const uint8_t* vrow = stg + v_off;
+            uint32_t words[16];
+            if (p.v_aligned) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 w4 = *reinterpret_cast<const uint4*>(vrow + 16 * c);
+                    words[4 * c] = w4.x; words[4 * c + 1] = w4.y; words[4 * c + 2] = w4.z; words[4 * c + 3] = w4.w;
+                }
+            } else {
+#pragma unroll
+                for (int w = 0; w < 16; ++w) words[w] = *reinterpret_cast<const uint32_t*>(vrow + 4 * w);
+            }
+            __syncwarp();                            // every lane holds its V row and norm in registers:
+            if (lane == 0) mbar_arrive(&sm.empty[this_stage]);  // this warp is done with the stage
+            // the V tile is free once the previous tile's P V has read it
+            if (it > 0 && !mbar_wait(&sm.bar_vfree, (it - 1) & 1)) { dead = true; break; }
+#pragma unroll
+            for (int w = 0; w < 16; ++w) {                 // 8 head-dims = one 32-bit index word per chunk
+                uint32_t lo0, hi0, lo1, hi1;
+                lookup4<VB>(tb, words[w], lo0, hi0);
+                lookup4<VB>(tb, words[w] >> 16, lo1, hi1);
+                *reinterpret_cast<uint4*>(v_dst + w * 128) =
+                    make_uint4(prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
+                               prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
+            }
+            fence_async_proxy();
+            mbar_arrive(&sm.vready);
+            if (advance(vw)) seq_len = max(__ldg(p.seq_lens + vw.seq), 0);
         }
         if (dead) st_volatile_shared(&sm.dead, 1);
     }
@@ -1316,9 +1397,16 @@ static const DecodeEnv& decode_env() {
 // else the four regions, each widened to 16-byte boundaries.
 static void plan_staging(DecodeParams& p) {
     const int ttok = p.ttok;
+    // Row pitch of an index region: widened by 16-byte steps (the copy reads that much more of the slot)
+    // until consecutive tokens' 16-byte chunks fall into different shared-memory banks, i.e. the pitch
+    // in words is an odd multiple of 4 modulo 32.
+    auto conflict_free = [&](int w, int x_max) {
+        while (((w / 4) % 32) % 8 != 4 && x_max + w + 16 <= p.total_bytes) w += 16;
+        return w;
+    };
     if (p.ht == p.H) {
         p.n_regions = 1;
-        p.reg_w[0] = (136 * p.H + 15) / 16 * 16;
+        p.reg_w[0] = conflict_free((136 * p.H + 15) / 16 * 16, 0);
         p.reg_base[0] = 0;
         for (int r = 1; r < kRegions; ++r) { p.reg_w[r] = 0; p.reg_base[r] = 0; }
         p.stage_bytes = ttok * p.reg_w[0];
@@ -1327,12 +1415,14 @@ static void plan_staging(DecodeParams& p) {
         int base = 0;
         for (int r = 0; r < kRegions; ++r) {
             const int len = ((r & 1) ? 4 : kHalfDim) * p.ht;
-            int off_max = 0;
+            int off_max = 0, x_max = 0;
             for (int h0 = 0; h0 < p.H; h0 += p.ht) {
                 const RegionWindow rw = region_window(p.H, h0);
                 off_max = std::max(off_max, rw.start[r] - rw.x[r]);
+                x_max = std::max(x_max, rw.x[r]);
             }
             p.reg_w[r] = (off_max + len + 15) / 16 * 16;
+            if ((r & 1) == 0) p.reg_w[r] = conflict_free(p.reg_w[r], x_max);
             p.reg_base[r] = base;
             base += ttok * p.reg_w[r];
         }

@@ -2,9 +2,9 @@
 ``rotorquant_vllm.triton`` package, calling librq_b200.so through its C ABI."""
 
 from .compress import compress_and_store, iso_compress, planar_compress
-from .decode import decode_workspace_bytes, fused_paged_rq_decode
+from .decode import decode_workspace_bytes, fused_paged_rq_decode, reserve_decode_workspace
 from .decompress import decompress_blocks, decompress_cache_paged, iso_decompress, planar_decompress
-from .prefill import fused_paged_rq_int8_prefill
+from .prefill import fused_paged_rq_int8_prefill, reserve_prefill_scratch
 from .rotation import validate_rotation
 
 __all__ = [
@@ -18,5 +18,7 @@ __all__ = [
     "fused_paged_rq_decode",
     "fused_paged_rq_int8_prefill",
     "decode_workspace_bytes",
+    "reserve_decode_workspace",
+    "reserve_prefill_scratch",
     "validate_rotation",
 ]

@@ -23,12 +23,28 @@ def decode_workspace_bytes(num_seqs: int, num_q_heads: int, num_kv_heads: int, h
 
 def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
     """Per-device scratch buffer, grown on demand.  Calls on one stream reuse it safely; callers
-    that run decode on several streams at once must pass their own ``workspace``."""
+    that run decode on several streams at once must pass their own ``workspace``.  Growing it
+    while a CUDA graph is being captured is refused: the allocation would be an error, and graphs
+    captured earlier would keep pointing at the buffer that is dropped -- reserve the largest batch
+    first (:func:`reserve_decode_workspace`)."""
     buf = _WORKSPACE.get(dev)
     if buf is None or buf.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(
+                f"rotorquant_vllm: decode needs {nbytes} bytes of scratch during a CUDA graph capture but only "
+                f"{0 if buf is None else buf.numel()} are reserved; call reserve_decode_workspace() for the largest "
+                "batch before capturing")
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
         _WORKSPACE[dev] = buf
     return buf
+
+
+def reserve_decode_workspace(dev: torch.device, num_seqs: int, num_q_heads: int, num_kv_heads: int,
+                             head_dim: int, max_seq_len: int) -> int:
+    """Put the scratch of the largest decode batch in place now; returns its size in bytes."""
+    need = decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim, max_seq_len)
+    _workspace(torch.device(dev), need)
+    return need
 
 
 def fused_paged_rq_decode(

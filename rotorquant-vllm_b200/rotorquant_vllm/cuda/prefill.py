@@ -42,10 +42,12 @@ def fused_paged_rq_int8_prefill(
 
     Two implementations give the same result: the fused kernel rebuilds the K/V tiles for every
     block of query rows; the staged one (``rq_prefill_int8_staged``) decompresses every tile once
-    into scratch memory first.  ``staged=None`` picks the staged path when a bound on the sequence
-    lengths is known -- ``max_seq_len``, else the width of the block table -- and the scratch stays
-    under 1 GiB; ``workspace`` (uint8) may supply the scratch, otherwise one buffer per device is
-    kept and grown as needed.
+    into scratch memory first.  The scratch is ``num_seqs * ceil(bound / 128) * H * 49664`` bytes
+    with ``bound`` = ``max_seq_len``, else the width of the block table.  ``staged=None`` picks the
+    staged path when the caller lends a ``workspace`` (uint8), or when the scratch fits the buffer
+    kept per device -- reserved up front by :func:`reserve_prefill_scratch`, grown on demand up to
+    ``SCRATCH_CAP`` bytes but never while a CUDA graph is being captured -- and the fused kernel
+    otherwise, so that no call allocates beyond the cap.
     """
     num_tokens, hq, d = q.shape
     assert d == head_dim
@@ -87,7 +89,7 @@ def fused_paged_rq_int8_prefill(
     bound = int(max_seq_len) if max_seq_len else block_table.shape[1] * block_size
     need = lib.rq_prefill_workspace_bytes(num_seqs, num_kv_heads, bound)
     if staged is None:
-        staged = workspace is not None or bool(max_seq_len) or need <= (1 << 30)
+        staged = workspace is not None or _scratch_available(dev, need)
     common = (
         q.data_ptr(), result.data_ptr(), _lib.dtype_code(q.dtype), q.stride(0), q.stride(1),
         result.stride(0), result.stride(1),
@@ -113,6 +115,22 @@ def fused_paged_rq_int8_prefill(
 
 
 _SCRATCH: dict = {}
+SCRATCH_CAP = 1 << 30          # the per-device buffer never grows beyond this many bytes
+
+
+def reserve_prefill_scratch(dev: torch.device, nbytes: int) -> None:
+    """Allocate the per-device scratch of the staged path now (at most ``SCRATCH_CAP`` bytes), so
+    that later calls inside the serving loop find it in place."""
+    _scratch(torch.device(dev), min(int(nbytes), SCRATCH_CAP))
+
+
+def _scratch_available(dev: torch.device, nbytes: int) -> bool:
+    """True when ``nbytes`` of scratch are in place, or may be put in place now (under the cap and
+    not inside a graph capture, where allocating is an error)."""
+    buf = _SCRATCH.get(dev)
+    if buf is not None and buf.numel() >= nbytes:
+        return True
+    return nbytes <= SCRATCH_CAP and not torch.cuda.is_current_stream_capturing()
 
 
 def _scratch(dev: torch.device, nbytes: int) -> torch.Tensor:

@@ -263,6 +263,7 @@ class RQAttentionImpl(FlashAttentionImpl):
         self._max_model_len = vllm_config.model_config.max_model_len if vllm_config is not None else 8192
         self._max_prefill_len = (vllm_config.scheduler_config.max_num_batched_tokens
                                  if vllm_config is not None else 2048)
+        self._max_num_seqs = (vllm_config.scheduler_config.max_num_seqs if vllm_config is not None else 256)
         _parse_rq_fused_paged_env()
         self._fused_paged_available = _fused_paged_kernel_available
         self._fused_prefill_available = _fused_prefill_kernel_available
@@ -286,16 +287,24 @@ class RQAttentionImpl(FlashAttentionImpl):
         self._total_bytes = _rq_total_bytes(self.head_size, h)
 
     def _init_cg_buffers(self, kv_cache: torch.Tensor, compute_dtype: torch.dtype) -> None:
-        """Reserve the decode scratch once, sized for ``max_model_len``, so that no allocation
-        happens later (for instance inside a CUDA graph capture)."""
-        from rotorquant_vllm.cuda.decode import _workspace, decode_workspace_bytes
+        """Reserve the scratch of both kernels once, before serving starts, so that no ``forward``
+        allocates later (for instance inside a CUDA graph capture): the decode scratch for the
+        largest batch the scheduler admits (``max_num_seqs``) at the longest context the cache can
+        hold, and the prefill staging buffer for one batch of ``max_num_batched_tokens`` tokens
+        (bounded by the launcher's cap; larger batches take the kernel that needs no scratch)."""
+        from rotorquant_vllm.cuda.decode import reserve_decode_workspace
+        from rotorquant_vllm.cuda.prefill import reserve_prefill_scratch
 
         num_blocks, block_size, _ = kv_cache.shape
         max_tokens = min(self._max_model_len, num_blocks * block_size)
-        max_seqs = max(1, min(self._max_prefill_len, 1024))
-        need = decode_workspace_bytes(max_seqs, self.num_heads, self.num_kv_heads, self.head_size,
-                                      max_tokens)
-        _workspace(kv_cache.device, need)
+        # the launcher bounds sequence lengths by (block-table width x block size): whole blocks
+        max_tokens = (max_tokens + block_size - 1) // block_size * block_size
+        reserve_decode_workspace(kv_cache.device, max(1, self._max_num_seqs), self.num_heads, self.num_kv_heads,
+                                 self.head_size, max_tokens)
+        lib = _rq_lib.lib()
+        prefill_seqs = max(1, min(self._max_num_seqs, self._max_prefill_len // 128 + 1))
+        reserve_prefill_scratch(kv_cache.device,
+                                lib.rq_prefill_workspace_bytes(prefill_seqs, self.num_kv_heads, self._max_prefill_len))
         self._cg_buffers_ready = True
 
     # -- cache write -------------------------------------------------------------------------
