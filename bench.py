@@ -419,7 +419,9 @@ class GpuJob:
         torch.cuda.synchronize(self.dev)
         out = self.out.cpu()
         kc, vc, R = self.kc.cpu(), self.vc.cpu(), self.R.cpu()
-        picks = sorted({0, len(self.seq_lens_host) - 1, len(self.seq_lens_host) // 2})[:sample_seqs]
+        n_seqs = len(self.seq_lens_host)
+        k = max(1, min(sample_seqs, n_seqs))
+        picks = sorted({round(i * (n_seqs - 1) / max(k - 1, 1)) for i in range(k)})   # evenly spread, ends included
         worst, over, rows = 0.0, 0, 0
         for s in picks:
             n = int(self.seq_lens_host[s])

@@ -4,43 +4,35 @@
 // Triton kernel (one program per (sequence, query head), CUDA-core dot products, no split-KV)
 // and the two dense 128x128 rotations its launcher runs around it.
 //
-// Work decomposition.  A tile is 128 (token, KV head) pairs: T = 128 / Ht consecutive tokens of one
-// sequence times a "head tile" of Ht KV heads (Ht = all KV heads of this GPU when there are 1, 2, 4
-// or 8 of them).  With a whole head tile in one CTA the payload of a token -- K indices, K norms,
-// V indices, V norms of all its heads, 136 * H contiguous bytes of the slot -- arrives as ONE row of
-// ONE TMA box per block of tokens, norms included.  (One CTA per KV head, as the first versions had
-// it, needs a 64-byte K row, a 64-byte V row and two norm sectors per token and head: about 4.5
-// memory requests for 136 bytes.  The SM's TMA unit was measured at 0.17 such rows per cycle, 16-byte
-// cp.async copies at about 0.2, against 0.75 requests per cycle at the HBM roofline.)
-// The (sequence, tile) space of the batch is one line of tiles, cut into contiguous pieces; a CTA
-// streams the tiles of one piece for one (head tile, group of up to 8 query heads per KV head) and
-// leaves one partial result per sequence its piece touches.  A second launch merges the partial
-// results of every (sequence, query head), rounds, and applies R.
+// Work decomposition.  A tile is 128 consecutive tokens of one sequence and one KV head.  The
+// (sequence, tile) space of the batch is one line of tiles, cut into contiguous pieces; a CTA
+// streams the tiles of one piece for one (KV head, group of up to 8 query heads) and leaves one
+// partial result per sequence its piece touches.  The 136 payload bytes of a (token, KV head) are
+// read from HBM exactly once for all query heads of the GQA group.  A second launch merges the
+// partial results of every (sequence, query head), rounds, and applies R.  Up to 128 sequences the
+// attention CTAs compute the tile prefix sums themselves; larger batches get a one-CTA plan launch.
 //
-// The attention CTA is warp specialised.  Two threads work on every pair: thread t of the four K
-// warps (which owns TMEM lane t) builds the pair's K digit planes, reads its scores and runs the
-// softmax; thread t of the four V warps decompresses the pair's V row into the shared V tile at the
-// same time.  Two more warps own the asynchronous engines.  Issuing a tcgen05.mma of these skinny
-// shapes keeps the issuing thread busy for 100 (S^T, N = 64) to 140 cycles (O^T) whatever else runs, and
-// two threads of different warps issue side by side without slowing each other, so one warp issues the
-// S^T MMAs and fills the ring of staged tiles with TMA boxes, the other issues the O^T MMAs, each when the
-// other warps have published its operands.  No block-wide barrier is met inside the tile loop;
-// everything is ordered by mbarriers.
+// The attention CTA has 128 threads, one per token of the tile and per TMEM lane; four CTAs share
+// an SM, which is what keeps the SM's issue slots busy while any one CTA waits on its tensor-core
+// or memory steps.  (Warp-specialised variants with separate issuer, copy, K and V warps and two
+// CTAs per SM were built and measured: every one of them was slower, because fewer threads are
+// left for the byte permutes that bound the kernel.)
 //
 // Arithmetic (matches "reference decompress + SDPA"):
 //   q_rot   = round_T(q @ R^T)            exact FMA chain per 4x4 block, computed per part
-//   K, V    = round_T(centroid[idx]*norm) exactly the decompressed values: each pair gets a
+//   K, V    = round_T(centroid[idx]*norm) exactly the decompressed values: each token gets a
 //             table of its 8/16 rounded products, elements are fetched from it with PRMT
 //   scores  = int8 tensor-core mma over 15-bit integer images of q_rot and K (exact for K, 2^-14
-//             of the row maximum for q): S^T = K Q^T with the 128 pairs on the M side and the digit
-//             planes of ALL query heads of the head tile on the N side; a pair reads the columns of
-//             its own KV head.  fp32 scaling, exp2-domain softmax against a reference maximum per
-//             head (exact maximum of the part's first tile; it moves later only when a score
-//             exceeds it by 2^8)
+//             of the row maximum for q): S^T = K Q^T with the 128 tokens on the M side, the K
+//             digit planes as a TMEM A operand and the query digit planes as the shared B operand;
+//             fp32 scaling, exp2-domain softmax against a reference maximum per head (it moves
+//             only when a score exceeds it by 2^8)
 //   P @ V   = tensor-core mma with P split into hi + lo parts (two T-precision terms, ~16 bits),
-//             fp32 accumulate in tensor memory; the 16 pairs of one MMA k-step belong to one KV
-//             head, so each k-step accumulates into that head's output columns
+//             fp32 accumulate in tensor memory: O^T += V^T [P hi | P lo]
 //   out     = round_T(round_T(o / l) @ R)  in the merge kernel
+// The kernel is bound by the dequantisation instructions (one byte permute per V value, half of
+// one per K value), not by tensor throughput.
+
 #include <cuda.h>          // CUtensorMap (types only; the encoder is looked up at run time)
 
 #include <algorithm>
@@ -54,22 +46,12 @@
 
 namespace rq {
 
-constexpr int kQPerHead = 8;                 // query-head slots per KV head of a partial row / of one item
-constexpr int kPairs = 128;                  // (token, KV head) pairs per tile = compute threads per CTA
-constexpr int kComputeThreads = 128;
-constexpr int kDecodeThreads = 320;          // K warps 0..3, V warps 4..7, two issuer warps
-constexpr int kVWarp0 = 4;
-constexpr int kSIssuerWarp = 8;              // issues S^T = K Q^T and the TMA copies
-constexpr int kPvIssuerWarp = 9;             // issues O^T += V^T P
-constexpr uint32_t kTmemCols = 256;          // columns allocated per CTA
-constexpr uint32_t kColKhi = 0, kColKlo = 32, kColS = 64, kColS2 = 128, kColO = 192;
-constexpr int kMaxCols = 64;                 // columns of one S accumulator and of O: head tile x 2 x query heads
-constexpr int kInlinePlanSeqs = 256;         // up to this many sequences the CTAs scan seq_lens themselves
+constexpr int kHeadsPerCta = 8;              // query-head slots of a partial row / of one item
+constexpr int kQPerHead = kHeadsPerCta;
+constexpr int kTokenBox = 16;                // tokens per TMA box (never straddles a block of 16 or more)
+constexpr int kInlinePlanSeqs = 128;         // up to this many sequences the CTAs scan seq_lens themselves
 constexpr int kMaxLayers = 4;                // launch layers with their own piece weight
-constexpr int kCtasPerSm = 2;
-constexpr int kRingBytes = 54 * 1024;        // staged tiles (two or three stages)
-constexpr int kMaxStages = 3;
-constexpr int kRegions = 4;                  // K indices, K norms, V indices, V norms
+constexpr int kCtasPerSm = 4;
 
 struct DecodeParams {
     const void* q;
@@ -87,45 +69,21 @@ struct DecodeParams {
     float qk_scale;                        // sm_scale * log2(e)
     int H, Hq, G;                          // KV heads, query heads, Hq / H
     int head_groups;                       // ceil(G / 8)
-    int ht, ht_shift;                      // KV heads per tile (1, 2, 4 or 8)
-    int ttok, ttok_shift;                  // tokens per tile = 128 / ht
-    int n_cols;                            // columns of S and of O: max(16, ht * 2 * NH)
-    float* ws_o;                           // [row][ht * 8 slots][128], row = (group + sequence) * J + item
-    float* ws_m;                           // [row][ht * 8]
+    float* ws_o;                           // [row][8 slots][128], row = (group + sequence) * J + item
+    float* ws_m;                           // [row][8]
     float* ws_l;
     void* out;
     int64_t o_stride_seq, o_stride_head;
     int32_t* prefix;                       // [num_seqs + 1] exclusive prefix of tiles per sequence (workspace)
     int num_seqs;
-    int groups;                            // pieces; CTA = (group, item)
+    int groups;                            // pieces; CTA = (group, item), item = (KV head, head group)
     int inline_plan;                       // the attention CTAs compute the prefix sums themselves
     int bs_shift;                          // log2(block_size) when it is a power of two, else -1
-    // staging: a stage holds, per region, an array [ttok][w] of the region's bytes of every token
-    int n_regions;                         // 1: the whole payload of the head tile is contiguous; else 4
-    int reg_w[kRegions];                   // bytes copied per token and region (multiple of 16)
-    int reg_base[kRegions];                // offset of the region's array inside a stage
-    int stage_bytes, stages;
-    int box_rows;                          // tokens per TMA box (0: no TMA, the issuer warp copies 4-byte words)
-    int v_aligned;                         // V rows sit on 16-byte boundaries of the stage
     int layer_ctas;                        // CTAs per launch layer (SM count) when pieces are weighted, else 0
     int num_layers;
     int layer_w[kMaxLayers];               // piece weight of the CTAs of each launch layer
-    unsigned long long* trace;             // development builds only
 };
 
-// Development builds (-DRQ_DECODE_TRACE) record clock64() at the phase boundaries of a few CTAs.
-#ifdef RQ_DECODE_TRACE
-#define RQ_TRACE(point)                                                                             \
-    do {                                                                                            \
-        if (trace_row != nullptr && lane == 0 && it < 64) trace_row[it * 16 + (point)] = clock64(); \
-    } while (0)
-#else
-#define RQ_TRACE(point) \
-    do {                \
-    } while (0)
-#endif
-
-// ---- pieces -----------------------------------------------------------------------------------
 //
 // On one SM the CTAs that were launched first (lower block index) get the larger share of the
 // issue slots while several run side by side, so equal pieces would finish far apart.  CTA c
@@ -145,21 +103,6 @@ __host__ __device__ inline int64_t weight_cum(int64_t n, int layer_ctas, int num
 __device__ __forceinline__ int64_t piece_begin(const DecodeParams& p, int64_t g, int64_t total, int J) {
     return total * weight_cum(g * J, p.layer_ctas, p.num_layers, p.layer_w) /
            weight_cum(static_cast<int64_t>(p.groups) * J, p.layer_ctas, p.num_layers, p.layer_w);
-}
-
-// Byte ranges of the four payload regions of head tile `h0 .. h0 + ht` inside a slot of H heads:
-// start[r] (may be 4, 8 or 12 bytes past a 16-byte boundary) and the 16-byte boundary below it.
-struct RegionWindow {
-    int start[kRegions], x[kRegions];
-};
-__host__ __device__ inline RegionWindow region_window(int H, int h0) {
-    RegionWindow rw;
-    rw.start[0] = kHalfDim * h0;                       // K indices
-    rw.start[1] = kHalfDim * H + 4 * h0;               // K norms
-    rw.start[2] = (kHalfDim + 4) * H + kHalfDim * h0;  // V indices
-    rw.start[3] = (2 * kHalfDim + 4) * H + 4 * h0;     // V norms
-    for (int r = 0; r < kRegions; ++r) rw.x[r] = rw.start[r] & ~15;
-    return rw;
 }
 
 // ---- small PTX wrappers ------------------------------------------------------
@@ -220,13 +163,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
-// 4-byte asynchronous copy global -> shared; the mbarrier receives one arrival (already counted in
-// its expected arrivals) when every copy this thread has issued so far has landed.
+// 4-byte asynchronous copy global -> shared.
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
@@ -236,22 +175,10 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
-// Barrier of the 128 compute threads only (the issuer warp never joins it).
-__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
 // Programmatic dependent launch: the merge kernel may be scheduled while the attention kernel
 // drains; it must not read the partial results before this wait returns.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-__device__ __forceinline__ int ld_volatile_shared(const int* p) {
-    int v;
-    asm volatile("ld.volatile.shared.b32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_volatile_shared(int* p, int v) {
-    asm volatile("st.volatile.shared.b32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
-}
 
 // ---- per-token lookup tables -------------------------------------------------
 //
@@ -344,766 +271,564 @@ __device__ __forceinline__ Table<BITS> build_value_table(const float* cb, float 
     return t;
 }
 
-// ---- shared memory of the attention CTA ---------------------------------------------------------
-struct DecodeSmem {
-    alignas(128) uint16_t v[kPairs * kHeadDim];        // V tile: core (pair/8)*16 + pos/8, core row pair%8
-    uint16_t p[kPairs * 16];                           // P tile: core (pair/8)*2 + n/8, core row pair%8
-    uint8_t q[kMaxCols * kHeadDim];                    // Q digit planes, K-major: core (n/8)*8 + pos/16
-    alignas(16) float cb[2][16];
-    float qf[32];                                      // per (head of the tile, query head): q unscale * sm_scale * log2(e)
-    float mref[32];                                    // reference maxima, kept by the first lane of every head
-    float alpha[32];                                   // rescale factors of a moved reference
-    float red_m[8][kQPerHead];                         // per half warp (16 pairs of one head)
-    float red_l[8][kQPerHead];
-    int scan[4];
-    uint64_t full[kMaxStages];                         // copy warp -> K / V warps: "the tile's rows landed"
-    uint64_t empty[kMaxStages];                        // K / V warps -> copy warp: rows read (8 arrivals: one per warp)
-    uint64_t kready, pvready, vready;                  // K / V warps -> issuer: operands published (128 arrivals each)
-    uint64_t bar_s, bar_o, bar_vfree, bar_drain, bar_drain2;   // issuers -> K / V warps: MMAs complete
+// ---- the attention kernel ---------------------------------------------------------------------
+//
+// One CTA = 128 threads = 128 tokens of a tile; thread t owns token t of the tile and TMEM lane t.
+// Per tile:
+//   1. the thread builds the K and V tables of its token and turns the 128 K indices into the two
+//      signed digit planes of the 15-bit integer image (32 registers each), which it stores into
+//      its TMEM lane: the K tile never touches shared memory;
+//   2. S^T = K Q^T on the tcgen05 int8 path with the K planes as the TMEM A operand and the query
+//      digit planes (rows 0..7 high digits of the 8 heads, rows 8..15 low digits) as a 2 KB shared
+//      B operand: two accumulators of 16 columns (K high x [Q high | Q low], K low x [..]);
+//   3. meanwhile the thread decompresses the V row of its token into the shared V tile, in the
+//      core-matrix order of an MN-major operand (the tensor core does the transposition);
+//   4. each thread reads the 32 sums of its token, forms the G scores, exponentiates against a
+//      CTA-wide lazy reference maximum per head (it moves only when a score exceeds it by 2^8,
+//      found with one block vote), and writes its probabilities, split into hi + lo parts of T
+//      precision, as 16 values of the shared P tile;
+//   5. O^T += V^T [P hi | P lo] on the tcgen05 16-bit path: 128 head-dim lanes x 16 columns.
+// Index rows reach the CTA as TMA boxes of 16 tokens x 64 bytes (64-byte swizzle), staged per warp
+// one tile ahead; norms are read straight from global memory.  Caches whose geometry rules TMA out
+// (block sizes that are not a power of two >= 16) are read with direct 16-byte loads instead, and
+// V rows that do not start on 16-byte boundaries (1 or 2 KV heads) with 4-byte cp.async.
+
+constexpr int kUTile = 128;                  // tokens per tile
+constexpr int kUThreads = 128;
+constexpr int kUCtasPerSm = kCtasPerSm;
+constexpr uint32_t kUTmemCols = 128;         // columns allocated per CTA
+constexpr uint32_t kUColKhi = 0, kUColKlo = 32, kUColS = 64, kUColO = 96;
+
+struct __align__(512) UmmaSmem {
+    uint8_t stage[4][2][32 * kHalfDim];      // per warp: K | V index rows of its 32 tokens of the next tile
+                                             // (TMA, 64-byte swizzle: chunk c of row r at c ^ ((r >> 1) & 3))
+    uint16_t v[kUTile * kHeadDim];           // V tile: core (token/8)*16 + pos/8, core row token%8
+    uint16_t p[kUTile * 16];                 // P tile: core (token/8)*2 + n/8, core row token%8
+    uint8_t q[16 * kHeadDim];                // Q digit planes, K-major: core (n/8)*8 + pos/16
+    float cb[2][16];
+    float qf[kHeadsPerCta];                  // q unscale * sm_scale * log2(e) per head
+    float red[4][kHeadsPerCta];              // cross-warp reductions
+    int32_t prefix[kInlinePlanSeqs + 1];     // tile prefix sums when the CTA plans for itself
+    int32_t scan[4];
+    uint64_t bar_s, bar_o;
+    uint64_t bar_in[4];                      // per warp: "staged rows landed"
     uint32_t tmem_base;
-    int grow_tile, redo_tile, dead;
-    int32_t prefix[kInlinePlanSeqs + 1];
-    alignas(1024) uint8_t ring[kRingBytes];            // stages of [region][token][bytes]
 };
 
-struct TmaMaps {
-    CUtensorMap m[kRegions];
-};
-
-// Position on the line of tiles: walks the parts (piece x sequence) of one piece.
-struct Walk {
-    int seq, tile, t_end;     // current sequence, tile inside it, end of the part
-    int64_t x;                // linear position of (seq, tile)
-};
-
-// First sequence s with prefix[s + 1] > x (x < prefix[n]).
-__device__ __forceinline__ int find_seq(const int32_t* prefix, int n, int64_t x) {
-    int lo = 0, hi = n - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi) >> 1;
-        if (prefix[mid + 1] > x) hi = mid;
-        else lo = mid + 1;
-    }
-    return lo;
-}
-
-// NH = query heads computed per KV head: 4 when the GQA group has at most 4 heads, else 8.
-template <typename T, int KB, int VB, int NH>
-__global__ void __launch_bounds__(kDecodeThreads, kCtasPerSm)
-decode_attn_kernel(const DecodeParams p, const __grid_constant__ TmaMaps maps) {
+// NH = query heads computed per item: 4 when the GQA group has at most 4 heads, else 8.
+// MODE = how the index rows reach the CTA: 0 direct global loads by every thread, 1 TMA boxes for K and
+// V rows, 2 TMA boxes for the K rows and 4-byte cp.async for V rows that are not 16-byte aligned.
+template <typename T, int KB, int VB, int MODE, int NH>
+__global__ void __launch_bounds__(kUThreads, kUCtasPerSm)
+decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_idx) {
+    constexpr bool TMA = MODE != 0;
+    constexpr bool v_by_tma = MODE == 1;
     extern __shared__ uint8_t smem_raw[];
-    DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
+    // aligned by hand: the swizzled TMA rows want 512-byte alignment
+    UmmaSmem& sm = *reinterpret_cast<UmmaSmem*>(smem_raw + ((512u - (smem_u32(smem_raw) & 511u)) & 511u));
     constexpr int NK = 1 << KB, NV = 1 << VB;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int J = (p.H >> p.ht_shift) * p.head_groups;
-    const int64_t group = blockIdx.x / J;
-    const int item = static_cast<int>(blockIdx.x % J);
-    const int S = p.stages;
 
-    // ---- set-up: barriers, tensor memory, codebooks, tile prefix sums, a zero P tile ----
-    if (tid == 0) {
-        for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(&sm.full[s], p.box_rows > 0 ? 1 : 32);
-            mbar_init(&sm.empty[s], 8);
-        }
-        mbar_init(&sm.kready, kComputeThreads);
-        mbar_init(&sm.pvready, kComputeThreads);
-        mbar_init(&sm.vready, kComputeThreads);
-        mbar_init(&sm.bar_s, 1);
-        mbar_init(&sm.bar_o, 1);
-        mbar_init(&sm.bar_vfree, 1);
-        mbar_init(&sm.bar_drain, 1);
-        mbar_init(&sm.bar_drain2, 1);
-        sm.grow_tile = -1;
-        sm.redo_tile = -1;
-        sm.dead = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    // P columns a pair never writes (the other KV head's half of its 16 columns) must read as zero
-    for (int i = tid; i < kPairs * 16 * 2 / 16; i += kDecodeThreads)
-        reinterpret_cast<uint4*>(sm.p)[i] = make_uint4(0u, 0u, 0u, 0u);
-    fence_async_proxy();
-    if (warp == 0) tmem_alloc(&sm.tmem_base, kTmemCols);
-    if (warp == kSIssuerWarp) {
-        const int kv = lane >> 4, i = lane & 15;
-        const int n = kv ? NV : NK;
-        sm.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
-    }
+    // ---- tiles of every sequence as an exclusive prefix sum ----
     const int32_t* prefix = p.prefix;
-    if (p.inline_plan) {
-        // two consecutive sequences per compute thread, warp scan, four warp totals
-        int a = 0, b = 0;
-        if (tid < kComputeThreads) {
-            const int s0 = 2 * tid;
-            if (s0 < p.num_seqs) a = (max(__ldg(p.seq_lens + s0), 0) + p.ttok - 1) >> p.ttok_shift;
-            if (s0 + 1 < p.num_seqs) b = (max(__ldg(p.seq_lens + s0 + 1), 0) + p.ttok - 1) >> p.ttok_shift;
-        }
-        int incl = a + b;
+    if (p.inline_plan) {                       // one sequence per thread, warp scan, four warp totals
+        const int n = tid < p.num_seqs ? (max(__ldg(p.seq_lens + tid), 0) + kUTile - 1) / kUTile : 0;
+        int incl = n;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const int v = __shfl_up_sync(0xffffffffu, incl, o);
             if (lane >= o) incl += v;
         }
-        if (lane == 31 && warp < 4) sm.scan[warp] = incl;
-        tc_fence_before();
+        if (lane == 31) sm.scan[warp] = incl;
         __syncthreads();
-        if (tid < kComputeThreads) {
-            int before = incl - (a + b);
-            for (int w = 0; w < warp; ++w) before += sm.scan[w];
-            const int s0 = 2 * tid;
-            if (s0 <= p.num_seqs) sm.prefix[s0] = before;
-            if (s0 + 1 <= p.num_seqs) sm.prefix[s0 + 1] = before + a;
-            if (s0 + 2 == p.num_seqs) sm.prefix[s0 + 2] = before + a + b;
-        }
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += sm.scan[w];
+        if (tid == 0) sm.prefix[0] = 0;
+        if (tid < p.num_seqs) sm.prefix[tid + 1] = before + incl;
+        __syncthreads();
         prefix = sm.prefix;
-    } else {
-        tc_fence_before();
+        if (blockIdx.x == 0)                   // the merge launch reads the prefix sums from the workspace
+            for (int i = tid; i <= p.num_seqs; i += kUThreads) p.prefix[i] = sm.prefix[i];
     }
+    if (tid == 0) grid_launch_dependents();    // the merge kernel may be scheduled; it waits for this grid's end
+
+    // ---- this CTA's piece: CTA = (group, item) ----
+    const int J = p.H * p.head_groups;
+    const int64_t total = prefix[p.num_seqs];
+    const int64_t group = blockIdx.x / J;
+    const int item = static_cast<int>(blockIdx.x % J);
+    if (group >= p.groups) return;
+    int64_t x = piece_begin(p, group, total, J);
+    const int64_t x_end = piece_begin(p, group + 1, total, J);
+    if (x >= x_end) return;
+
+    if (tid == 0) {
+        mbar_init(&sm.bar_s, 1);
+        mbar_init(&sm.bar_o, 1);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mbar_init(&sm.bar_in[w], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_proxy();
+    }
+    if (warp == 0) tmem_alloc(&sm.tmem_base, kUTmemCols);
+    if (tid < 32) {
+        const int kv = tid >> 4, i = tid & 15;
+        const int n = kv ? NV : NK;
+        sm.cb[kv][i] = i < n ? __ldg((kv ? p.cent_v : p.cent_k) + i) : 0.0f;
+    }
+    tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (p.inline_plan && blockIdx.x == 0)          // the merge launch reads the prefix sums from the workspace
-        for (int i = tid; i <= p.num_seqs; i += kDecodeThreads) p.prefix[i] = sm.prefix[i];
-
     const uint32_t tmem = sm.tmem_base;
-    const int64_t total = prefix[p.num_seqs];
-    const int64_t x0 = piece_begin(p, group, total, J);
-    const int64_t x_end = piece_begin(p, group + 1, total, J);
-    const bool has_work = group < p.groups && x0 < x_end;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lane quarter
 
-    const int hg = item % p.head_groups;
-    const int h0 = (item / p.head_groups) << p.ht_shift;            // first KV head of this CTA's head tile
-    const int heads_here = min(kQPerHead, p.G - hg * kQPerHead);     // query heads per KV head handled here
-    const int last_blk = static_cast<int>(p.num_blocks) - 1;
-    const RegionWindow rw = region_window(p.H, h0);
+    const SlotLayout lay = slot_layout(p.H);
+    const int v_align = (lay.v_idx % 16 == 0) ? 16 : ((lay.v_idx % 8 == 0) ? 8 : 4);
+    // S^T: s32 accumulator, int8 operands, N = 16, M = 128;  O^T: f32 accumulator, T operands, both MN-major
+    const uint32_t idesc_s = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+    const uint32_t idesc_o = (1u << 4) | (TcFormat<T>::kFmt << 7) | (TcFormat<T>::kFmt << 10) | (1u << 15) |
+                             (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+    const uint32_t q_addr = smem_u32(sm.q), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p);
+    uint8_t* const v_dst = reinterpret_cast<uint8_t*>(sm.v) + (tid >> 3) * (16 * 128) + (tid & 7) * 16;
+    uint8_t* const p_dst = reinterpret_cast<uint8_t*>(sm.p) + (tid >> 3) * (2 * 128) + (tid & 7) * 16;
 
-    auto start_walk = [&](Walk& w) {
-        w.x = x0;
-        w.seq = find_seq(prefix, p.num_seqs, x0);
-        const int pre = prefix[w.seq];
-        w.tile = static_cast<int>(x0 - pre);
-        const int64_t reach = w.tile + (x_end - x0);
-        const int n_s = prefix[w.seq + 1] - pre;
-        w.t_end = reach < n_s ? static_cast<int>(reach) : n_s;
-    };
-    // returns true when the new position is the first tile of a part
-    auto advance = [&](Walk& w) -> bool {
-        ++w.x;
-        ++w.tile;
-        if (w.tile < w.t_end || w.x >= x_end) return false;
-        do { ++w.seq; } while (w.seq < p.num_seqs - 1 && prefix[w.seq + 1] - prefix[w.seq] <= 0);
-        const int n_s = prefix[w.seq + 1] - prefix[w.seq];
-        const int64_t left = x_end - w.x;
-        w.tile = 0;
-        w.t_end = left < n_s ? static_cast<int>(left) : n_s;
-        return true;
-    };
+    // sequence holding position x: first s with prefix[s + 1] > x
+    int seq = 0;
+    for (int base = 0; base < p.num_seqs; base += 32) {
+        const int s = base + lane;
+        const int64_t end = s < p.num_seqs ? prefix[s + 1] : INT64_MAX;
+        const unsigned hit = __ballot_sync(0xffffffffu, end > x);
+        if (hit) { seq = base + __ffs(hit) - 1; break; }
+    }
 
-    bool dead = false;
-#ifdef RQ_DECODE_TRACE
-    // CTAs 0, 100 and 200: [cta][warp][tile][16 points]
-    unsigned long long* trace_row = nullptr;
-    if (p.trace != nullptr && blockIdx.x % 100 == 0 && blockIdx.x / 100 < 3 && (warp < kVWarp0 || warp == kSIssuerWarp))
-        trace_row = p.trace + ((blockIdx.x / 100) * 5 + (warp == kSIssuerWarp ? 4 : warp)) * 64 * 16;
-#endif
+    float cmax_k = 0.0f;                      // largest |K centroid|
+#pragma unroll
+    for (int i = 0; i < NK; ++i) cmax_k = fmaxf(cmax_k, fabsf(sm.cb[0][i]));
 
-    if (has_work && warp == kSIssuerWarp) {
-        // ============ S issuer + copy warp: S^T = K Q^T of every tile, and the rows of the tiles ahead ============
-        const uint32_t ncols = static_cast<uint32_t>(p.n_cols);
-        const uint32_t idesc_s = (2u << 4) | (1u << 7) | (1u << 10) | ((ncols >> 3) << 17) | ((128u >> 4) << 24);
-        const uint32_t q_addr = smem_u32(sm.q);
-        const uint32_t ring_addr = smem_u32(sm.ring);
+    uint32_t ph_s = 0, ph_o = 0;              // phase parities of the two barriers
+    [[maybe_unused]] uint32_t ph_in = 0;      // ... and of this warp's staging barrier
+    bool dead = false;                        // a bounded wait expired (same value in all threads)
+    // staged rows of this thread's token: 16-byte chunk c sits at chunk c ^ ((lane >> 1) & 3)
+    [[maybe_unused]] const uint8_t* const stage_k = sm.stage[warp][0] + lane * kHalfDim;
+    [[maybe_unused]] const uint8_t* const stage_v = sm.stage[warp][1] + lane * kHalfDim;
+    [[maybe_unused]] const uint32_t stage_sw = 16u * ((lane >> 1) & 3);
 
-        // ---- producer: the rows of one tile into ring stage (n % S) ----
-        // Lane b keeps the block-table entry of box b of the tile to be produced next, loaded right
-        // after the previous tile was issued.
-        Walk pw;
-        start_walk(pw);
-        int produced = 0;
-        int p_seq_len = max(__ldg(p.seq_lens + pw.seq), 0);
-        int p_blk = 0;
-        auto prefetch_blk = [&]() {
-            if (p.box_rows > 0 && pw.x < x_end) {
-                const int t = (pw.tile << p.ttok_shift) + lane * p.box_rows;
-                p_blk = (lane * p.box_rows < p.ttok && t < p_seq_len)
-                            ? __ldg(p.block_table + pw.seq * p.bt_stride + (t >> p.bs_shift)) : 0;
+#pragma unroll 1
+    while (x < x_end && seq < p.num_seqs) {
+        const int pre = prefix[seq], n_s = prefix[seq + 1] - pre;
+        if (n_s <= 0 || x >= static_cast<int64_t>(pre) + n_s) { ++seq; continue; }
+        const int t_begin = static_cast<int>(x - pre);
+        const int64_t reach = t_begin + (x_end - x);
+        const int t_end = reach < n_s ? static_cast<int>(reach) : n_s;
+        const int kvh = item / p.head_groups, hg = item % p.head_groups;
+        const int heads_here = min(kHeadsPerCta, p.G - hg * kHeadsPerCta);
+        const int first_qh = kvh * p.G + hg * kHeadsPerCta;
+        const int seq_len = max(__ldg(p.seq_lens + seq), 0);
+        const int32_t* bt_row = p.block_table + seq * p.bt_stride;
+        const int last_blk = static_cast<int>(p.num_blocks) - 1;
+
+        // Index words and norms of this thread's token, fetched one tile ahead.  Past the end of the
+        // sequence nothing is fetched and the norm is 0, which zeroes the value of every table entry;
+        // the words then keep their last contents, which must still be index words (a nibble with
+        // its top bit set would make PRMT return a sign mask instead of a table byte), hence the
+        // clearing here.
+        uint32_t kw[16], vw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { kw[i] = 0u; vw[i] = 0u; }
+        float nk = 0.0f, nv = 0.0f;
+        bool failed_in = false;
+
+        // ---- where this thread's token of a tile lives ----
+        // cp.async-free direct path: pointer to the token's K index row (nullptr past the end).
+        [[maybe_unused]] auto slot_of = [&](int tile) -> const uint8_t* {
+            const int tok = tile * kUTile + tid;
+            if (tok >= seq_len) return nullptr;
+            const int bi = p.bs_shift >= 0 ? (tok >> p.bs_shift) : (tok / p.block_size);
+            const int off = p.bs_shift >= 0 ? (tok & (p.block_size - 1)) : (tok % p.block_size);
+            int blk = __ldg(bt_row + bi);
+            blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
+            return p.cache + (static_cast<int64_t>(blk) * p.block_size + off) * p.total_bytes + kvh * kHalfDim;
+        };
+        [[maybe_unused]] auto fetch_direct = [&](int which, const uint8_t* slot, uint32_t (&w)[16], float& norm) {
+            norm = 0.0f;               // a zero norm makes every table entry zero: stale index words are harmless
+            if (slot != nullptr) {
+                if (which) load_idx64(slot + lay.v_idx, v_align, w);
+                else load_idx64(slot + lay.k_idx, 16, w);
+                norm = __ldg(reinterpret_cast<const float*>(slot + (which ? lay.v_norm : lay.k_norm) -
+                                                            kvh * (kHalfDim - 4)));
             }
         };
-        prefetch_blk();
-        auto produce = [&]() {
-            const int stage = produced % S;
-            const uint32_t bar = smem_u32(&sm.full[stage]);
-            const uint32_t dst0 = ring_addr + static_cast<uint32_t>(stage * p.stage_bytes);
-            const int tok0 = pw.tile << p.ttok_shift;
-            const int n_valid = min(p.ttok, p_seq_len - tok0);
-            if (p.box_rows > 0) {
-                const int n_box = (n_valid + p.box_rows - 1) / p.box_rows;       // at most 16: one per lane
-                int row_bytes = 0;
-                for (int r = 0; r < p.n_regions; ++r) row_bytes += p.reg_w[r];
-                if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_box * p.box_rows * row_bytes));
-                __syncwarp();
-                if (lane < n_box) {
-                    const int t = tok0 + lane * p.box_rows;
-                    const int blk = p_blk < 0 ? 0 : (p_blk > last_blk ? last_blk : p_blk);
-                    const int slot = (blk << p.bs_shift) + (t & (p.block_size - 1));
+        // TMA path.  A warp stages the index rows of its 32 tokens of the NEXT tile in shared memory
+        // (two 16-token boxes per region; a 16-token group never straddles a block).  Lane l keeps
+        // the block-table entry of its group (l / 16) for the tile after that, loaded a tile early,
+        // and the slot number of its own token in the staged tile (-1 past the end).
+        [[maybe_unused]] int pf_blk = 0, staged_slot = -1;
+        [[maybe_unused]] auto load_blk = [&](int tile) -> int {
+            const int t = tile * kUTile + 32 * warp + (lane & 16);
+            return (tile < t_end && t < seq_len) ? __ldg(bt_row + (t >> p.bs_shift)) : 0;
+        };
+        [[maybe_unused]] auto issue_tile = [&](int tile, int blk) {      // completes one phase of bar_in[warp]
+            const int t = tile * kUTile + 32 * warp + (lane & 16);
+            blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
+            const int gslot = (blk << p.bs_shift) + (t & (p.block_size - 1));
+            const int s0 = __shfl_sync(0xffffffffu, gslot, 0), s1 = __shfl_sync(0xffffffffu, gslot, 16);
+            const bool on0 = tile * kUTile + 32 * warp < seq_len, on1 = tile * kUTile + 32 * warp + 16 < seq_len;
+            staged_slot = (t + (lane & 15) < seq_len) ? gslot + (lane & 15) : -1;
+            if (lane == 0) {
+                const uint32_t bar = smem_u32(&sm.bar_in[warp]);
+                if (on0) {
+                    const uint32_t group_bytes = v_by_tma ? 2048u : 1024u;
+                    mbar_expect_tx(bar, on1 ? 2 * group_bytes : group_bytes);
+                    tma_load_2d(smem_u32(sm.stage[warp][0]), &map_idx, kvh * kHalfDim, s0, bar);
+                    if (v_by_tma) tma_load_2d(smem_u32(sm.stage[warp][1]), &map_idx, lay.v_idx + kvh * kHalfDim, s0, bar);
+                    if (on1) {
+                        tma_load_2d(smem_u32(sm.stage[warp][0]) + 1024u, &map_idx, kvh * kHalfDim, s1, bar);
+                        if (v_by_tma)
+                            tma_load_2d(smem_u32(sm.stage[warp][1]) + 1024u, &map_idx, lay.v_idx + kvh * kHalfDim, s1, bar);
+                    }
+                } else {
+                    mbar_arrive(&sm.bar_in[warp]);
+                }
+            }
+            if constexpr (!v_by_tma) {
+                // V rows that do not start on 16-byte boundaries (1 or 2 KV heads on this GPU): the warp
+                // copies them with 4-byte cp.async, two rows per instruction, into the same swizzled order
 #pragma unroll
-                    for (int r = 0; r < kRegions; ++r)
-                        if (r < p.n_regions)
-                            tma_load_2d(dst0 + p.reg_base[r] + lane * p.box_rows * p.reg_w[r], &maps.m[r],
-                                        (p.n_regions == 1 ? 0 : rw.x[r]) >> 3, slot, bar);
+                for (int i = 0; i < 16; ++i) {
+                    const int row = 2 * i + (lane >> 4), word = lane & 15;
+                    if (tile * kUTile + 32 * warp + row < seq_len) {
+                        const int slot = (i < 8 ? s0 : s1) + (row & 15);
+                        cp_async4(smem_u32(sm.stage[warp][1] + row * kHalfDim + (((word >> 2) ^ ((row >> 1) & 3)) << 4) + ((word & 3) << 2)),
+                                  p.cache + static_cast<int64_t>(slot) * p.total_bytes + lay.v_idx + kvh * kHalfDim + 4 * word);
+                    }
+                }
+            }
+        };
+        // the staged V rows are complete (the K rows are covered by the barrier)
+        [[maybe_unused]] auto v_rows_landed = [&]() {
+            if constexpr (!v_by_tma) {
+                cp_async_wait_all();
+                __syncwarp();
+            }
+        };
+        [[maybe_unused]] auto fetch_staged = [&](int which, uint32_t (&w)[16], float& norm) {
+            norm = 0.0f;
+            if (staged_slot >= 0) {
+                const uint8_t* rows = which ? stage_v : stage_k;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 x4 = *reinterpret_cast<const uint4*>(rows + ((16u * c) ^ stage_sw));
+                    w[4 * c] = x4.x; w[4 * c + 1] = x4.y; w[4 * c + 2] = x4.z; w[4 * c + 3] = x4.w;
+                }
+                norm = __ldg(reinterpret_cast<const float*>(
+                    p.cache + static_cast<int64_t>(staged_slot) * p.total_bytes + (which ? lay.v_norm : lay.k_norm) + 4 * kvh));
+            }
+        };
+        // the first tile's rows are requested before the query set-up, which hides most of their latency
+        if (!dead) {
+            if constexpr (TMA) {
+                issue_tile(t_begin, load_blk(t_begin));
+                pf_blk = load_blk(t_begin + 1);
+            } else {
+                const uint8_t* first = slot_of(t_begin);
+                fetch_direct(0, first, kw, nk);
+                fetch_direct(1, first, vw, nv);
+            }
+        }
+
+        // ---- queries of this item: rotate, round, quantise to signed digit planes (B operand) ----
+#pragma unroll 1
+        for (int round = 0; round < NH / 4; ++round) {
+            const int h = 4 * round + warp;
+            float r[4] = {0.f, 0.f, 0.f, 0.f};
+            if (h < heads_here) {
+                const T* qp = static_cast<const T*>(p.q) + seq * p.q_stride_seq +
+                              static_cast<int64_t>(first_qh + h) * p.q_stride_head + 4 * lane;
+                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(qp));
+                const float2 x01 = unpack_pair<T>(raw.x), x23 = unpack_pair<T>(raw.y);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 rr = __ldg(reinterpret_cast<const float4*>(
+                        p.rotation + (4 * lane + j) * kHeadDim + 4 * lane));
+                    float acc = __fmul_rn(x01.x, rr.x);
+                    acc = __fmaf_rn(x01.y, rr.y, acc);
+                    acc = __fmaf_rn(x23.x, rr.z, acc);
+                    acc = __fmaf_rn(x23.y, rr.w, acc);
+                    r[j] = round_to<T>(acc);
+                }
+            }
+            float mx = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const bool ok = mx >= 1.0e-30f && mx <= 3.0e38f;
+            const int e = ok ? exponent_of(mx) : 0;
+            const float scale = ok ? pow2i(13 - e) : 0.0f;
+            int qu[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) qu[j] = __float2int_rn(fmaf(r[j], scale, 128.0f));
+            // position x of a row holds head-dim x ^ 1 (the nibble order of the cache)
+            const uint32_t a = prmt(qu[1], qu[0], 0x5140), b = prmt(qu[3], qu[2], 0x5140);
+            const uint32_t off = (lane >> 2) * 128 + (h & 7) * 16 + 4 * (lane & 3);
+            *reinterpret_cast<uint32_t*>(&sm.q[off]) = prmt(a, b, 0x7632);                       // row h: high digits
+            *reinterpret_cast<uint32_t*>(&sm.q[1024 + off]) = prmt(a, b, 0x5410) ^ 0x80808080u;  // row 8 + h: low digits
+            if (lane == 0) sm.qf[h] = (ok ? pow2i(e - 13) : 0.0f) * p.qk_scale;
+        }
+        fence_async_proxy();
+        __syncthreads();
+
+        if constexpr (TMA) {
+            if (!dead) {
+                failed_in |= !mbar_wait(&sm.bar_in[warp], ph_in);
+                ph_in ^= 1u;
+                v_rows_landed();
+                fetch_staged(0, kw, nk);
+                fetch_staged(1, vw, nv);
+                __syncwarp();
+                if (t_begin + 1 < t_end) issue_tile(t_begin + 1, pf_blk);
+                pf_blk = load_blk(t_begin + 2);
+            }
+        }
+
+        float m_ref[NH], l_acc[NH];
+#pragma unroll
+        for (int h = 0; h < NH; ++h) { m_ref[h] = -INFINITY; l_acc[h] = 0.0f; }
+        bool pv_pending = false;
+
+#pragma unroll 1
+        for (int tile = t_begin; tile < t_end && !dead; ++tile) {
+            [[maybe_unused]] const uint8_t* next_slot = nullptr;
+            if constexpr (!TMA) next_slot = tile + 1 < t_end ? slot_of(tile + 1) : nullptr;
+            const bool valid = tile * kUTile + tid < seq_len;
+            bool failed = failed_in;
+            failed_in = false;
+
+            // ---- 1, 2: K table, digit planes -> TMEM, S^T = K Q^T ----
+            float k_unscale;
+            {
+                float cbk[NK];
+#pragma unroll
+                for (int i = 0; i < NK; i += 4) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(&sm.cb[0][i]);
+                    cbk[i] = c4.x; cbk[i + 1] = c4.y; cbk[i + 2] = c4.z; cbk[i + 3] = c4.w;
+                }
+                const Table<KB> tk = build_int_table<T, KB>(cbk, cmax_k, nk, k_unscale);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int w = 0; w < 8; ++w) {
+                        const uint32_t word = kw[8 * half + w];
+                        lookup4<KB>(tk, word, lo[2 * w], hi[2 * w]);
+                        lookup4<KB>(tk, word >> 16, lo[2 * w + 1], hi[2 * w + 1]);
+                    }
+                    tmem_st16_nowait(lane_base + kUColKhi + 16 * half, hi);
+                    tmem_st16_nowait(lane_base + kUColKlo + 16 * half, lo);
+                }
+            }
+            if constexpr (TMA) {
+                if (tile + 1 < t_end) {                  // the staged rows of the next tile
+                    failed |= !mbar_wait(&sm.bar_in[warp], ph_in);
+                    ph_in ^= 1u;
+                    fetch_staged(0, kw, nk);
                 }
             } else {
-                // any block size: 4-byte copies of every region's window, token by token
-                const int32_t* bt_row = p.block_table + pw.seq * p.bt_stride;
-                for (int r = 0; r < p.n_regions; ++r) {
-                    const int words = p.reg_w[r] >> 2;
-                    const int src_x = p.n_regions == 1 ? 0 : rw.x[r];
-                    for (int i = lane; i < n_valid * words; i += 32) {
-                        const int tt = i / words, wd = i - tt * words;
-                        const int t = tok0 + tt;
-                        const int bi = p.bs_shift >= 0 ? (t >> p.bs_shift) : (t / p.block_size);
-                        const int off = p.bs_shift >= 0 ? (t & (p.block_size - 1)) : (t % p.block_size);
-                        int blk = __ldg(bt_row + bi);
-                        blk = blk < 0 ? 0 : (blk > last_blk ? last_blk : blk);
-                        const uint8_t* slot = p.cache + (static_cast<int64_t>(blk) * p.block_size + off) * p.total_bytes;
-                        cp_async4(dst0 + p.reg_base[r] + tt * p.reg_w[r] + 4 * wd, slot + src_x + 4 * wd);
-                    }
-                }
-                cp_async_arrive(&sm.full[stage]);
+                fetch_direct(0, next_slot, kw, nk);
             }
-            __syncwarp();
-            ++produced;
-            if (advance(pw)) p_seq_len = max(__ldg(p.seq_lens + pw.seq), 0);
-            prefetch_blk();
-        };
-        // Tile n >= S may be copied once the K and the V warps have read the rows of tile n - S out of its
-        // stage.  Tiles the next iteration cannot do without are waited for; further ahead, a stage that
-        // is not free yet is simply tried again later.
-        auto produce_ahead = [&](int it_now) {
-            while (pw.x < x_end && !dead) {
-                const int n = produced;
-                if (n >= S) {
-                    const uint32_t parity = ((n / S) - 1) & 1;
-                    if (n <= it_now + 1) {
-                        if (!mbar_wait(&sm.empty[n % S], parity)) { dead = true; return; }
-                    } else if (!mbar_test(&sm.empty[n % S], parity)) {
-                        return;
-                    }
-                }
-                produce();
-            }
-        };
-        produce_ahead(-1);
-
-        Walk cw;
-        start_walk(cw);
-        int it = 0;
-#pragma unroll 1
-        for (; cw.x < x_end && !dead; ++it) {
-            // the digit planes of the tile are in tensor memory, the query planes in shared memory
-            RQ_TRACE(0);
-            if (!mbar_wait(&sm.kready, it & 1)) { dead = true; break; }
-            RQ_TRACE(1);
-            tc_fence_after();
-            if (lane == 0) {
+            tmem_wait_st();                              // the digit planes are in TMEM
+            tc_fence_before();
+            __syncthreads();
+            if (tid == 0) {
+                tc_fence_after();
 #pragma unroll
                 for (int s = 0; s < 4; ++s)
-                    tc_mma_i8_ta(tmem + kColS, tmem + kColKhi + 8 * s, smem_desc(q_addr + 256 * s, 128, 1024),
+                    tc_mma_i8_ta(tmem + kUColS, tmem + kUColKhi + 8 * s, smem_desc(q_addr + 256 * s, 128, 1024),
                                  idesc_s, s > 0 ? 1u : 0u);
 #pragma unroll
                 for (int s = 0; s < 4; ++s)
-                    tc_mma_i8_ta(tmem + kColS2, tmem + kColKlo + 8 * s, smem_desc(q_addr + 256 * s, 128, 1024),
+                    tc_mma_i8_ta(tmem + kUColS + 16, tmem + kUColKlo + 8 * s, smem_desc(q_addr + 256 * s, 128, 1024),
                                  idesc_s, s > 0 ? 1u : 0u);
                 tc_commit(&sm.bar_s);
             }
-            __syncwarp();
-            RQ_TRACE(2);
-            produce_ahead(it);
-            RQ_TRACE(5);
-            advance(cw);
-        }
-        if (dead) {
-            st_volatile_shared(&sm.dead, 1);
-            // copies still in flight: a bounded wait each, so that none lands after the CTA is gone
-            if (p.box_rows > 0)
-                for (int c = max(0, produced - S); c < produced; ++c) mbar_wait(&sm.full[c % S], (c / S) & 1);
-            if (lane == 0) tc_commit(&sm.bar_drain);
-            __syncwarp();
-            mbar_wait(&sm.bar_drain, 0);
-        }
-        cp_async_wait_all();
-    } else if (has_work && warp == kPvIssuerWarp) {
-        // ============ P V issuer: O^T += V^T [P hi | P lo], one k-step of 16 pairs (one KV head) at a time ============
-        const uint32_t idesc_o = (1u << 4) | (TcFormat<T>::kFmt << 7) | (TcFormat<T>::kFmt << 10) | (1u << 15) |
-                                 (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-        const uint32_t v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p);
-        Walk cw;
-        start_walk(cw);
-        bool first_in_part = true;
-        uint32_t ph_pv = 0;
-        int it = 0;
-        const int cols_per_head = 2 * NH;
-#pragma unroll 1
-        for (; cw.x < x_end; ++it) {
-            if (!mbar_wait(&sm.pvready, ph_pv)) { dead = true; break; }
-            ph_pv ^= 1u;
-            if (ld_volatile_shared(&sm.grow_tile) == it) {
-                // a score outgrew the reference maximum: hand the tile back; the K warps move the
-                // maxima, rescale, rewrite P and publish again
-                if (lane == 0) {
-                    st_volatile_shared(&sm.redo_tile, it);
-                    mbar_arrive(&sm.bar_o);
-                }
-                __syncwarp();
-                if (!mbar_wait(&sm.pvready, ph_pv)) { dead = true; break; }
-                ph_pv ^= 1u;
-            }
-            if (!mbar_wait(&sm.vready, it & 1)) { dead = true; break; }
-            tc_fence_after();
-            if (lane == 0) {
-                int prev_blk = -1;
-#pragma unroll
-                for (int s = 0; s < 8; ++s) {
-                    // output columns of the KV head of pairs 16 s .. 16 s + 15, as a block of 16
-                    const int blk16 = (((16 * s) >> p.ttok_shift) * cols_per_head) >> 4;
-                    const uint32_t acc = (first_in_part && blk16 != prev_blk) ? 0u : 1u;
-                    prev_blk = blk16;
-                    tc_mma_f16(tmem + kColO + 16 * blk16, smem_desc(v_addr + 4096 * s, 2048, 128),
-                               smem_desc(p_addr + 512 * s, 256, 128), idesc_o, acc);
-                }
-                tc_commit(&sm.bar_o);
-                tc_commit(&sm.bar_vfree);
-            }
-            __syncwarp();
-            first_in_part = advance(cw);
-        }
-        if (dead) {
-            st_volatile_shared(&sm.dead, 1);
-            if (lane == 0) tc_commit(&sm.bar_drain2);
-            __syncwarp();
-            mbar_wait(&sm.bar_drain2, 0);
-        }
-    } else if (has_work && warp < kVWarp0) {
-        // =========================== K warps: digit planes, scores, softmax ===========================
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lane quarter
-        const int hh = tid >> p.ttok_shift, tt = tid & (p.ttok - 1);      // this pair: KV head of the tile, token
-        const int half = tid >> 4;                                         // 16 pairs of one head
-        const int halves_per_head = p.ttok >> 4, first_half = (half / halves_per_head) * halves_per_head;
-        const int col16 = (hh * 2 * NH) & ~15, sub = (hh * 2 * NH) & 15;   // this head's columns: block of 16, offset
-        // P: this pair's row of 16 columns; with 4 query heads its 8 values fill one 8-column core
-        uint8_t* const p_dst = reinterpret_cast<uint8_t*>(sm.p) + (tid >> 3) * (2 * 128) + (tid & 7) * 16 +
-                               (NH == 4 ? (sub >> 3) * 128 : 0);
-        // where this pair's bytes sit inside a stage
-        int f_off[kRegions];
-#pragma unroll
-        for (int r = 0; r < kRegions; ++r) {
-            const int unit = (r & 1) ? 4 : kHalfDim;
-            f_off[r] = p.n_regions == 1 ? tt * p.reg_w[0] + rw.start[r] + unit * hh
-                                        : p.reg_base[r] + tt * p.reg_w[r] + (rw.start[r] - rw.x[r]) + unit * hh;
-        }
-        float cmax_k = 0.0f;
-#pragma unroll
-        for (int i = 0; i < NK; ++i) cmax_k = fmaxf(cmax_k, fabsf(sm.cb[0][i]));
 
-        uint32_t ph_o = 0;
-        int it = 0;                                // tiles streamed by this CTA so far
-        int stage = 0;                             // it % S, and the parity of that stage's "landed" barrier
-        uint32_t ph_full = 0;
-        int64_t x = x0;
-        int seq = find_seq(prefix, p.num_seqs, x0);
-
-#pragma unroll 1
-        while (x < x_end && seq < p.num_seqs && !dead) {
-            const int pre = prefix[seq], n_s = prefix[seq + 1] - pre;
-            if (n_s <= 0 || x >= static_cast<int64_t>(pre) + n_s) { ++seq; continue; }
-            const int t_begin = static_cast<int>(x - pre);
-            const int64_t reach = t_begin + (x_end - x);
-            const int t_end = reach < n_s ? static_cast<int>(reach) : n_s;
-            const int seq_len = max(__ldg(p.seq_lens + seq), 0);
-
-            // ---- queries of this part: rotate, round, quantise to signed digit planes (B operand) ----
-            // rows of head j of the tile: 2 NH j + g (high digits of query head g), 2 NH j + NH + g (low digits)
-#pragma unroll 1
-            for (int jq = warp; jq < (NH << p.ht_shift); jq += 4) {
-                const int j = jq / NH, g = jq % NH;
-                float r[4] = {0.f, 0.f, 0.f, 0.f};
-                if (g < heads_here) {
-                    const int qh = (h0 + j) * p.G + hg * kQPerHead + g;
-                    const T* qp = static_cast<const T*>(p.q) + seq * p.q_stride_seq +
-                                  static_cast<int64_t>(qh) * p.q_stride_head + 4 * lane;
-                    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(qp));
-                    const float2 x01 = unpack_pair<T>(raw.x), x23 = unpack_pair<T>(raw.y);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float4 rr = __ldg(reinterpret_cast<const float4*>(
-                            p.rotation + (4 * lane + k) * kHeadDim + 4 * lane));
-                        float acc = __fmul_rn(x01.x, rr.x);
-                        acc = __fmaf_rn(x01.y, rr.y, acc);
-                        acc = __fmaf_rn(x23.x, rr.z, acc);
-                        acc = __fmaf_rn(x23.y, rr.w, acc);
-                        r[k] = round_to<T>(acc);
-                    }
-                }
-                float mx = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-                const bool ok = mx >= 1.0e-30f && mx <= 3.0e38f;
-                const int e = ok ? exponent_of(mx) : 0;
-                const float scale = ok ? pow2i(13 - e) : 0.0f;
-                int qu[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) qu[k] = __float2int_rn(fmaf(r[k], scale, 128.0f));
-                // position x of a row holds head-dim x ^ 1 (the nibble order of the cache)
-                const uint32_t a = prmt(qu[1], qu[0], 0x5140), b = prmt(qu[3], qu[2], 0x5140);
-                const int row_hi = 2 * NH * j + g, row_lo = row_hi + NH;
-                const uint32_t in_row = (lane >> 2) * 128 + 4 * (lane & 3);
-                *reinterpret_cast<uint32_t*>(&sm.q[(row_hi >> 3) * 1024 + (row_hi & 7) * 16 + in_row]) = prmt(a, b, 0x7632);
-                *reinterpret_cast<uint32_t*>(&sm.q[(row_lo >> 3) * 1024 + (row_lo & 7) * 16 + in_row]) =
-                    prmt(a, b, 0x5410) ^ 0x80808080u;
-                if (lane == 0) sm.qf[NH * j + g] = (ok ? pow2i(e - 13) : 0.0f) * p.qk_scale;
-            }
-            fence_async_proxy();
-            compute_sync();
-
-            float m_ref[NH], l_acc[NH], l_pend[NH], sc[NH], qfk[NH];
-#pragma unroll
-            for (int g = 0; g < NH; ++g) {
-                m_ref[g] = -INFINITY; l_acc[g] = 0.0f; l_pend[g] = 0.0f; sc[g] = 0.0f;
-                qfk[g] = sm.qf[NH * hh + g];
-            }
-            bool pending = false;                    // a P V of this part has been requested and not yet awaited
-
-            // probabilities of the tile whose scores are in sc[], against the current reference maxima
-            auto emit_p = [&]() {
-#pragma unroll
-                for (int g = 0; g < NH; ++g) l_pend[g] = ex2_approx(sc[g] - m_ref[g]);
-                uint32_t ph[NH / 2], pl[NH / 2];
-#pragma unroll
-                for (int j = 0; j < NH / 2; ++j) {
-                    ph[j] = pack_pair<T>(l_pend[2 * j], l_pend[2 * j + 1]);
-                    const float2 back = unpack_pair<T>(ph[j]);
-                    pl[j] = pack_pair<T>(l_pend[2 * j] - back.x, l_pend[2 * j + 1] - back.y);
-                }
-                if constexpr (NH == 4) {
-                    *reinterpret_cast<uint4*>(p_dst) = make_uint4(ph[0], ph[1], pl[0], pl[1]);
-                } else {
-                    *reinterpret_cast<uint4*>(p_dst) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                    *reinterpret_cast<uint4*>(p_dst + 128) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-                }
-                fence_async_proxy();
-            };
-            // maximum of sc[] over the pairs of this thread's KV head -> m_new[]
-            auto head_max = [&](float (&m_new)[NH]) {
-#pragma unroll
-                for (int g = 0; g < NH; ++g) {
-                    float m = sc[g];
-#pragma unroll
-                    for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                    if ((lane & 15) == 0) sm.red_m[half][g] = m;
-                }
-                compute_sync();
-#pragma unroll
-                for (int g = 0; g < NH; ++g) {
-                    float m = sm.red_m[first_half][g];
-                    for (int i = 1; i < halves_per_head; ++i) m = fmaxf(m, sm.red_m[first_half + i][g]);
-                    m_new[g] = m;
-                }
-                compute_sync();                      // red_m may be rewritten from here on
-            };
-            // Wait for the P V of tile `it - 1`; if the issuer handed the tile back because a score
-            // outgrew the reference, move the maxima, rescale the sums, publish P again and wait again.
-            auto settle_pending = [&]() {
-                if (!mbar_wait(&sm.bar_o, ph_o)) { dead = true; return; }
+            // ---- 3: V row -> shared tile (the previous tile's P V must have read it) ----
+            if (pv_pending) {
+                failed |= !mbar_wait(&sm.bar_o, ph_o);
                 ph_o ^= 1u;
                 tc_fence_after();
-                if (ld_volatile_shared(&sm.redo_tile) == it - 1) {
-                    float m_new[NH];
-                    head_max(m_new);
+            }
+            uint32_t d[32];                              // the 32 sums of this token (see step 4)
+            {
+                float cbv[NV];
 #pragma unroll
-                    for (int g = 0; g < NH; ++g) {
-                        m_new[g] = fmaxf(m_new[g], m_ref[g]);
-                        const float a = ex2_approx(m_ref[g] - m_new[g]);
-                        l_acc[g] *= a;
-                        m_ref[g] = m_new[g];
-                        if (tt == 0) { sm.alpha[NH * hh + g] = a; sm.mref[NH * hh + g] = m_new[g]; }
-                    }
-                    compute_sync();
-                    // O^T: lane = head-dim, column 2 NH j + g (+ NH: the lo part) = query head g of head j
-                    for (int c0 = 0; c0 < p.n_cols; c0 += 16) {
-                        uint32_t o[16];
-                        tmem_ld16_nowait(lane_base + kColO + c0, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const int col = c0 + c, j = col / (2 * NH), g = col % NH;
-                            const float a = j < p.ht ? sm.alpha[NH * j + g] : 1.0f;
-                            o[c] = __float_as_uint(__uint_as_float(o[c]) * a);
-                        }
-                        tmem_st16_nowait(lane_base + kColO + c0, o);
-                    }
-                    tmem_wait_st();
-                    emit_p();
-                    tc_fence_before();
-                    mbar_arrive(&sm.pvready);
-                    if (!mbar_wait(&sm.bar_o, ph_o)) { dead = true; return; }
-                    ph_o ^= 1u;
-                    tc_fence_after();
+                for (int i = 0; i < NV; i += 4) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(&sm.cb[1][i]);
+                    cbv[i] = c4.x; cbv[i + 1] = c4.y; cbv[i + 2] = c4.z; cbv[i + 3] = c4.w;
                 }
+                const Table<VB> tb = build_value_table<T, VB>(cbv, nv);
 #pragma unroll
-                for (int g = 0; g < NH; ++g) l_acc[g] += l_pend[g];
-                pending = false;
-            };
-
-#pragma unroll 1
-            for (int tile = t_begin; tile < t_end; ++tile, ++it) {
-                const bool valid = (tile << p.ttok_shift) + tt < seq_len;
-                const uint8_t* stg = sm.ring + stage * p.stage_bytes;
-                const int this_stage = stage;
-                RQ_TRACE(0);
-                if (!mbar_wait(&sm.full[stage], ph_full)) { dead = true; break; }
-                if (++stage == S) { stage = 0; ph_full ^= 1u; }
-                RQ_TRACE(1);
-
-                // ---- K table, digit planes -> tensor memory ----
-                float k_unscale;
-                {
-                    // a zero norm makes every table entry zero: pairs past the end contribute nothing
-                    const float nk = valid ? *reinterpret_cast<const float*>(stg + f_off[1]) : 0.0f;
-                    float cbk[NK];
-#pragma unroll
-                    for (int i = 0; i < NK; i += 4) {
-                        const float4 c4 = *reinterpret_cast<const float4*>(&sm.cb[0][i]);
-                        cbk[i] = c4.x; cbk[i + 1] = c4.y; cbk[i + 2] = c4.z; cbk[i + 3] = c4.w;
+                for (int c = 0; c < 16; ++c) {       // 8 head-dims = one 32-bit index word per chunk
+                    if (c == 8) {
+                        // S^T is normally complete by now: request this token's sums so that the TMEM
+                        // read runs under the second half of the V row
+                        failed |= !mbar_wait(&sm.bar_s, ph_s);
+                        ph_s ^= 1u;
+                        tc_fence_after();
+                        tmem_ld32_nowait(lane_base + kUColS, d);
                     }
-                    const Table<KB> tk = build_int_table<T, KB>(cbk, cmax_k, nk, k_unscale);
-                    const uint8_t* krow = stg + f_off[0];
-#pragma unroll
-                    for (int hf = 0; hf < 2; ++hf) {
-                        const uint4 w0 = *reinterpret_cast<const uint4*>(krow + 32 * hf);
-                        const uint4 w1 = *reinterpret_cast<const uint4*>(krow + 32 * hf + 16);
-                        const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                        uint32_t hi[16], lo[16];
-#pragma unroll
-                        for (int w = 0; w < 8; ++w) {
-                            lookup4<KB>(tk, words[w], lo[2 * w], hi[2 * w]);
-                            lookup4<KB>(tk, words[w] >> 16, lo[2 * w + 1], hi[2 * w + 1]);
-                        }
-                        tmem_st16_nowait(lane_base + kColKhi + 16 * hf, hi);
-                        tmem_st16_nowait(lane_base + kColKlo + 16 * hf, lo);
-                    }
+                    uint32_t lo0, hi0, lo1, hi1;
+                    lookup4<VB>(tb, vw[c], lo0, hi0);
+                    lookup4<VB>(tb, vw[c] >> 16, lo1, hi1);
+                    *reinterpret_cast<uint4*>(v_dst + c * 128) =
+                        make_uint4(prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
+                                   prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
                 }
-                RQ_TRACE(2);
-                __syncwarp();                        // every lane holds its K row and norm in registers:
-                if (lane == 0) mbar_arrive(&sm.empty[this_stage]);   // this warp is done with the stage
-                tmem_wait_st();
+            }
+            if constexpr (TMA) {
+                v_rows_landed();
+                if (tile + 1 < t_end) fetch_staged(1, vw, nv);
+                __syncwarp();                            // the staging rows are free again
+                if (tile + 2 < t_end) issue_tile(tile + 2, pf_blk);
+                pf_blk = load_blk(tile + 3);
+            } else {
+                fetch_direct(1, next_slot, vw, nv);
+            }
+
+            // ---- 4: scores, lazy reference maximum, probabilities ----
+            float sc[NH];
+            const float tok_bias = valid ? 0.0f : -INFINITY;
+            {
+                tmem_wait_ld();
+                tmem_ld32_landed(d);
+                const float4 qf0 = *reinterpret_cast<const float4*>(&sm.qf[0]);
+                const float4 qf1 = *reinterpret_cast<const float4*>(&sm.qf[4]);
+                const float qf[8] = {qf0.x, qf0.y, qf0.z, qf0.w, qf1.x, qf1.y, qf1.z, qf1.w};
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    // d[h] = Khi.Qhi, d[8+h] = Khi.Qlo, d[16+h] = Klo.Qhi, d[24+h] = Klo.Qlo
+                    const int t1 = static_cast<int>(d[h]) * 256 + (static_cast<int>(d[8 + h]) + static_cast<int>(d[16 + h]));
+                    const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(static_cast<int>(d[24 + h])));
+                    // heads beyond the group have factor 0: they behave like heads with all-zero scores and
+                    // their columns are never written out; tokens past the end get -inf (probability 0)
+                    sc[h] = fmaf(f, qf[h] * k_unscale, tok_bias);
+                }
+            }
+            bool grow = false;
+#pragma unroll
+            for (int h = 0; h < NH; ++h) grow |= sc[h] > m_ref[h] + 8.0f;
+            // The probabilities are written on the assumption that no reference maximum moves; the
+            // block votes at the barrier that the P V issue needs anyway, and in the rare other case
+            // the maxima are moved and the probabilities written again.
+            float pr[NH];
+            auto emit_p = [&]() {
+#pragma unroll
+                for (int h = 0; h < NH; ++h) pr[h] = ex2_approx(sc[h] - m_ref[h]);
+                uint32_t ph[4] = {0u, 0u, 0u, 0u}, pl[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                for (int j = 0; j < NH / 2; ++j) {
+                    ph[j] = pack_pair<T>(pr[2 * j], pr[2 * j + 1]);
+                    const float2 back = unpack_pair<T>(ph[j]);
+                    pl[j] = pack_pair<T>(pr[2 * j] - back.x, pr[2 * j + 1] - back.y);
+                }
+                *reinterpret_cast<uint4*>(p_dst) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                *reinterpret_cast<uint4*>(p_dst + 128) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                fence_async_proxy();
                 tc_fence_before();
-                mbar_arrive(&sm.kready);
-                RQ_TRACE(3);
-
-                // ---- the previous tile's P V must be complete before P is rewritten (and may hand the tile back) ----
-                if (pending) {
-                    settle_pending();
-                    if (dead) break;
+            };
+            emit_p();
+            if (__syncthreads_or(grow || failed)) {
+                if (__syncthreads_or(failed)) { dead = true; break; }
+                // move the reference maxima: CTA-wide maximum per head, rescale sums and O^T
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    float m = sc[h];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                    if (lane == 0) sm.red[warp][h] = m;
                 }
-                RQ_TRACE(4);
-                uint32_t d1[16], d2[16];                     // this pair's sums: 16 columns of each accumulator
-                RQ_TRACE(5);
-                if (!mbar_wait(&sm.bar_s, it & 1)) { dead = true; break; }
-                RQ_TRACE(6);
-                tc_fence_after();
-                tmem_ld16_nowait(lane_base + kColS + col16, d1);
-                tmem_ld16_nowait(lane_base + kColS2 + col16, d2);
-
-                // ---- scores, reference maxima, probabilities ----
-                const float tok_bias = valid ? 0.0f : -INFINITY;
-                RQ_TRACE(7);
-                {
+                __syncthreads();
+                float alpha[kHeadsPerCta];
+#pragma unroll
+                for (int h = NH; h < kHeadsPerCta; ++h) alpha[h] = 1.0f;
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    const float m_tile = fmaxf(fmaxf(sm.red[0][h], sm.red[1][h]), fmaxf(sm.red[2][h], sm.red[3][h]));
+                    const float m_new = fmaxf(m_ref[h], m_tile);
+                    alpha[h] = (m_new == -INFINITY) ? 1.0f : ex2_approx(m_ref[h] - m_new);   // 0 on the first tile
+                    l_acc[h] *= alpha[h];
+                    m_ref[h] = m_new;
+                }
+                if (tile > t_begin) {                // O^T holds a sum: lane = head-dim, column = head (hi | lo)
+                    uint32_t o[16];
+                    tmem_ld16_nowait(lane_base + kUColO, o);
                     tmem_wait_ld();
-                    RQ_TRACE(8);
-                    tmem_ld16_landed(d1);
-                    tmem_ld16_landed(d2);
 #pragma unroll
-                    for (int g = 0; g < NH; ++g) {
-                        // columns of this head: sub + g = Q high digits of query head g, sub + NH + g = low digits
-                        int hh_, hl_, lh_, ll_;
-                        if constexpr (NH == 4) {
-                            hh_ = static_cast<int>(sub ? d1[8 + g] : d1[g]);
-                            hl_ = static_cast<int>(sub ? d1[12 + g] : d1[4 + g]);
-                            lh_ = static_cast<int>(sub ? d2[8 + g] : d2[g]);
-                            ll_ = static_cast<int>(sub ? d2[12 + g] : d2[4 + g]);
-                        } else {
-                            hh_ = static_cast<int>(d1[g]); hl_ = static_cast<int>(d1[8 + g]);
-                            lh_ = static_cast<int>(d2[g]); ll_ = static_cast<int>(d2[8 + g]);
-                        }
-                        const int t1 = hh_ * 256 + (hl_ + lh_);
-                        const float f = fmaf(static_cast<float>(t1), 256.0f, static_cast<float>(ll_));
-                        // query heads beyond the group have factor 0: they behave like heads with all-zero scores
-                        // and their columns are never written out; pairs past the end get -inf (probability 0)
-                        sc[g] = fmaf(f, qfk[g] * k_unscale, tok_bias);
-                    }
-                }
-                if (tile == t_begin) {
-                    // first tile of the part: the reference maxima are the exact maxima of this tile
-                    float m_new[NH];
-                    head_max(m_new);
-#pragma unroll
-                    for (int g = 0; g < NH; ++g) {
-                        m_ref[g] = m_new[g];
-                        if (tt == 0) sm.mref[NH * hh + g] = m_new[g];
-                    }
-                } else {
-                    bool grow = false;
-#pragma unroll
-                    for (int g = 0; g < NH; ++g) grow |= sc[g] > m_ref[g] + 8.0f;
-                    // rare: ask the issuer to hand the tile back instead of issuing its P V
-                    if (grow) st_volatile_shared(&sm.grow_tile, it);
+                    for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c & 7]);
+                    tmem_st16_nowait(lane_base + kUColO, o);
+                    tmem_wait_st();
                 }
                 emit_p();
-                tc_fence_before();
-                mbar_arrive(&sm.pvready);
-                RQ_TRACE(9);
-                pending = true;
+                __syncthreads();
             }
-            if (dead) break;
+#pragma unroll
+            for (int h = 0; h < NH; ++h) l_acc[h] += pr[h];
 
-            // ---- partial result of this part -> workspace row (group + sequence) * J + item ----
-            if (pending) {
-                settle_pending();
-                if (dead) break;
-            }
+            // ---- 5: O^T += V^T [P hi | P lo] ----
+            if (tid == 0) {
+                tc_fence_after();
 #pragma unroll
-            for (int g = 0; g < NH; ++g) {
-                float v = l_acc[g];
-#pragma unroll
-                for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if ((lane & 15) == 0) sm.red_l[half][g] = v;
+                for (int s = 0; s < 8; ++s)
+                    tc_mma_f16(tmem + kUColO, smem_desc(v_addr + 4096 * s, 2048, 128),
+                               smem_desc(p_addr + 512 * s, 256, 128), idesc_o, (tile > t_begin || s > 0) ? 1u : 0u);
+                tc_commit(&sm.bar_o);
             }
-            compute_sync();
-            const int64_t row = (group + seq) * J + item;
-            const int slots = p.ht * kQPerHead;
-            if (tid < p.ht * NH) {
-                const int j = tid / NH, g = tid % NH;
-                if (g < heads_here) {
-                    float l = 0.0f;
-                    for (int i = 0; i < halves_per_head; ++i) l += sm.red_l[j * halves_per_head + i][g];
-                    p.ws_m[row * slots + j * kQPerHead + g] = sm.mref[NH * j + g];
-                    p.ws_l[row * slots + j * kQPerHead + g] = l;
-                }
-            }
-            for (int c0 = 0; c0 < p.ht * 2 * NH; c0 += 16) {
-                uint32_t o[16];
-                tmem_ld16_nowait(lane_base + kColO + c0, o);
-                tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    // columns come in groups of 2 NH per head: NH hi parts, then NH lo parts
-                    if ((c % (2 * NH)) < NH) {
-                        const int j = (c0 + c) / (2 * NH), g = c % NH;
-                        if (g < heads_here && j < p.ht)      // lane (position) x holds head-dim x ^ 1
-                            p.ws_o[((row * slots + j * kQPerHead + g) << 7) + (tid ^ 1)] =
-                                __uint_as_float(o[c]) + __uint_as_float(o[c + NH]);
-                    }
-                }
-            }
-            tc_fence_before();
-            compute_sync();                          // red_l, the query planes and O^T are free for the next part
+            pv_pending = true;
+        }
 
-            x += t_end - t_begin;
-            if (t_end == n_s) ++seq;
+        // ---- partial result of this part -> workspace row (group + sequence) * J + item ----
+        if (pv_pending) {
+            const bool failed = !mbar_wait(&sm.bar_o, ph_o);
+            ph_o ^= 1u;
+            tc_fence_after();
+            if (__syncthreads_or(failed)) dead = true;
         }
-        if (dead) st_volatile_shared(&sm.dead, 1);
-    } else if (has_work) {
-        // =========================== V warps: V rows -> shared V tile ===========================
-        const int pair = tid - 32 * kVWarp0;
-        uint8_t* const v_dst = reinterpret_cast<uint8_t*>(sm.v) + (pair >> 3) * (16 * 128) + (pair & 7) * 16;
-        const int hh = pair >> p.ttok_shift, tt = pair & (p.ttok - 1);
-        const int unit_v = kHalfDim;
-        const int v_off = p.n_regions == 1 ? tt * p.reg_w[0] + rw.start[2] + unit_v * hh
-                                           : p.reg_base[2] + tt * p.reg_w[2] + (rw.start[2] - rw.x[2]) + unit_v * hh;
-        const int vn_off = p.n_regions == 1 ? tt * p.reg_w[0] + rw.start[3] + 4 * hh
-                                            : p.reg_base[3] + tt * p.reg_w[3] + (rw.start[3] - rw.x[3]) + 4 * hh;
-        Walk vw;
-        start_walk(vw);
-        int seq_len = max(__ldg(p.seq_lens + vw.seq), 0);
-        int stage = 0;
-        uint32_t ph_full = 0;
-#pragma unroll 1
-        for (int it = 0; vw.x < x_end; ++it) {
-            const bool valid = (vw.tile << p.ttok_shift) + tt < seq_len;
-            const uint8_t* stg = sm.ring + stage * p.stage_bytes;
-            const int this_stage = stage;
-            if (!mbar_wait(&sm.full[stage], ph_full)) { dead = true; break; }
-            if (++stage == S) { stage = 0; ph_full ^= 1u; }
-            float cbv[NV];
 #pragma unroll
-            for (int i = 0; i < NV; i += 4) {
-                const float4 c4 = *reinterpret_cast<const float4*>(&sm.cb[1][i]);
-                cbv[i] = c4.x; cbv[i + 1] = c4.y; cbv[i + 2] = c4.z; cbv[i + 3] = c4.w;
-            }
-            Table<VB> tb = build_value_table<T, VB>(cbv, *reinterpret_cast<const float*>(stg + vn_off));
-            if (!valid) {
-                // rows past the end of the sequence may hold bytes that are not index nibbles; with an
-                // all-zero table every PRMT result is zero whatever the selector (a -0.0 entry would
-                // turn a selector with its top bit set into a sign mask, i.e. a NaN pattern in fp16)
+        for (int h = 0; h < NH; ++h) {
+            float v = l_acc[h];
 #pragma unroll
-                for (int r = 0; r < Table<VB>::kRegs; ++r) tb.r[r] = 0u;
-            }
-            const uint8_t* vrow = stg + v_off;
-            uint32_t words[16];
-            if (p.v_aligned) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 w4 = *reinterpret_cast<const uint4*>(vrow + 16 * c);
-                    words[4 * c] = w4.x; words[4 * c + 1] = w4.y; words[4 * c + 2] = w4.z; words[4 * c + 3] = w4.w;
-                }
-            } else {
-#pragma unroll
-                for (int w = 0; w < 16; ++w) words[w] = *reinterpret_cast<const uint32_t*>(vrow + 4 * w);
-            }
-            __syncwarp();                            // every lane holds its V row and norm in registers:
-            if (lane == 0) mbar_arrive(&sm.empty[this_stage]);  // this warp is done with the stage
-            // the V tile is free once the previous tile's P V has read it
-            if (it > 0 && !mbar_wait(&sm.bar_vfree, (it - 1) & 1)) { dead = true; break; }
-#pragma unroll
-            for (int w = 0; w < 16; ++w) {                 // 8 head-dims = one 32-bit index word per chunk
-                uint32_t lo0, hi0, lo1, hi1;
-                lookup4<VB>(tb, words[w], lo0, hi0);
-                lookup4<VB>(tb, words[w] >> 16, lo1, hi1);
-                *reinterpret_cast<uint4*>(v_dst + w * 128) =
-                    make_uint4(prmt(lo0, hi0, 0x5140), prmt(lo0, hi0, 0x7362),
-                               prmt(lo1, hi1, 0x5140), prmt(lo1, hi1, 0x7362));
-            }
-            fence_async_proxy();
-            mbar_arrive(&sm.vready);
-            if (advance(vw)) seq_len = max(__ldg(p.seq_lens + vw.seq), 0);
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) sm.red[warp][h] = v;
         }
-        if (dead) st_volatile_shared(&sm.dead, 1);
+        __syncthreads();
+        const int64_t row = (group + seq) * J + item;
+        if (tid < heads_here) {
+            float m = m_ref[0];
+#pragma unroll
+            for (int h = 1; h < NH; ++h) m = tid == h ? m_ref[h] : m;
+            const float l = (sm.red[0][tid] + sm.red[1][tid]) + (sm.red[2][tid] + sm.red[3][tid]);
+            p.ws_m[row * kHeadsPerCta + tid] = m;
+            p.ws_l[row * kHeadsPerCta + tid] = dead ? __int_as_float(0x7fc00000) : l;
+        }
+        if (!dead) {
+            uint32_t o[16];
+            tmem_ld16_nowait(lane_base + kUColO, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int h = 0; h < NH; ++h)               // lane (position) x holds head-dim x ^ 1
+                if (h < heads_here)
+                    p.ws_o[(row * kHeadsPerCta + h) * kHeadDim + (tid ^ 1)] =
+                        __uint_as_float(o[h]) + __uint_as_float(o[8 + h]);
+        }
+        tc_fence_before();
+        __syncthreads();
+
+        x += t_end - t_begin;
+        if (t_end == n_s) ++seq;
     }
 
-    if (tid == 0) grid_launch_dependents();
     tc_fence_before();
     __syncthreads();
-    if (has_work && ld_volatile_shared(&sm.dead) != 0) {
-        // A bounded wait expired somewhere in this CTA: every part of its piece is marked invalid
-        // (NaN row sum), which the merge turns into NaN outputs.
-        int64_t x = x0;
-        int seq = find_seq(prefix, p.num_seqs, x0);
-        const int slots = p.ht * kQPerHead;
-        while (x < x_end && seq < p.num_seqs) {
-            const int pre = prefix[seq], n_s = prefix[seq + 1] - pre;
-            if (n_s <= 0 || x >= static_cast<int64_t>(pre) + n_s) { ++seq; continue; }
-            const int64_t left = x_end - x, in_seq = static_cast<int64_t>(pre) + n_s - x;
-            const int64_t row = (group + seq) * J + item;
-            if (tid < slots) {
-                p.ws_m[row * slots + tid] = 0.0f;
-                p.ws_l[row * slots + tid] = __int_as_float(0x7fc00000);
-            }
-            x += left < in_seq ? left : in_seq;
-            ++seq;
-        }
-    }
-    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+    if (warp == 0) tmem_dealloc(tmem, kUTmemCols);
 }
-
 // Tiles of every sequence as an exclusive prefix sum, for batches too large for the attention CTAs
 // to scan themselves: prefix[s] = sum_{s' < s} ceil(len[s'] / tile_tokens), prefix[num_seqs] = total.
 __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num_seqs, int tile_tokens,
@@ -1136,7 +861,7 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num
 // Merge: one warp per (sequence, query head), lane l owns head-dims 4l..4l+3 (one 4x4 block of R).
 // The parts of a (sequence, head) are the groups whose pieces overlap the sequence's tile range;
 // part (group, sequence) of item j lives at row (group + sequence) * J + j, and inside the row the
-// query head sits in slot (KV head within its tile) * 8 + (query head within its group of 8).  Lanes
+// query head sits in slot (query head within its group of 8).  Lanes
 // gather the running maxima and row sums of up to 32 parts at a time; then the warp sums the
 // weighted partial outputs.
 constexpr int kMergeWarps = 4;
@@ -1148,11 +873,11 @@ decode_merge_kernel(const DecodeParams p) {
     const int64_t wq = static_cast<int64_t>(blockIdx.x) * kMergeWarps + (threadIdx.x >> 5);
     if (wq >= static_cast<int64_t>(p.num_seqs) * p.Hq) return;
     const int seq = static_cast<int>(wq / p.Hq), qh = static_cast<int>(wq % p.Hq);
-    const int J = (p.H >> p.ht_shift) * p.head_groups;
+    const int J = p.H * p.head_groups;
     const int kvh = qh / p.G, hl = qh % p.G;
-    const int item = (kvh >> p.ht_shift) * p.head_groups + hl / kQPerHead;
-    const int slots = p.ht * kQPerHead;
-    const int slot = (kvh & (p.ht - 1)) * kQPerHead + hl % kQPerHead;
+    const int item = kvh * p.head_groups + hl / kQPerHead;
+    constexpr int slots = kQPerHead;
+    const int slot = hl % kQPerHead;
     const int64_t a = p.prefix[seq], n = p.prefix[seq + 1] - a, total = p.prefix[p.num_seqs];
 
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1237,10 +962,6 @@ static int env_int(const char* name, int fallback) {
     return (e != nullptr && e[0] != '\0') ? std::atoi(e) : fallback;
 }
 
-#ifdef RQ_DECODE_TRACE
-static unsigned long long* g_trace_buffer = nullptr;
-#endif
-
 // SM count of the current device (148 on a B200), looked up once per device.
 static int sm_count() {
     static std::mutex mu;
@@ -1256,32 +977,24 @@ static int sm_count() {
     return cached[dev];
 }
 
-// Tile geometry and scratch of one decode call.  A tile holds `ht` KV heads x 128 / ht tokens; the
-// (sequence, tile) space is cut into `groups` pieces and each piece is walked by J CTAs, one per
-// (head tile, group of 8 query heads per KV head).
+// Grid and scratch of one decode call.  The (sequence, tile) space is cut into `groups` pieces and
+// each piece is walked by J CTAs, one per (KV head, group of 8 query heads).
 struct DecodePlan {
-    int nh;                // query heads computed per KV head and item: 4 or 8
-    int ht, ht_shift;      // KV heads per tile
+    int nh;                // query heads computed per item: 4 or 8
     int J;                 // items
     int groups;            // pieces
-    size_t rows;           // partial-result rows: (group + sequence) * J + item, ht * 8 slots each
+    size_t rows;           // partial-result rows: (group + sequence) * J + item, 8 slots each
     size_t prefix_bytes;
     size_t bytes;
 };
-// The head tile: the largest of 1, 2, 4, 8 that divides the KV heads and whose query heads fit the
-// 64 accumulator columns (2 digit planes x nh query heads per KV head).  `forced` > 0 asks for that
-// many pieces per sequence.
+// One 128-token tile per piece at least; at most four CTAs per SM.  `forced` > 0 asks for that many
+// pieces per sequence.
 static DecodePlan plan_decode(int num_seqs, int H, int G, int max_seq_len, int forced) {
     DecodePlan pl;
     pl.nh = G <= 4 ? 4 : 8;
-    pl.ht = 1;
-    pl.ht_shift = 0;
-    for (int c = 2, s = 1; c <= 8; c <<= 1, ++s)
-        if (H % c == 0 && c * 2 * pl.nh <= kMaxCols) { pl.ht = c; pl.ht_shift = s; }
     const int head_groups = (G + kQPerHead - 1) / kQPerHead;
-    pl.J = (H / pl.ht) * head_groups;
-    const int ttok = kPairs / pl.ht;
-    const long long max_tiles = max_seq_len > 0 ? (max_seq_len + ttok - 1) / ttok : 1;
+    pl.J = H * head_groups;
+    const long long max_tiles = max_seq_len > 0 ? (max_seq_len + kUTile - 1) / kUTile : 1;
     const long long work = 1LL * num_seqs * max_tiles;
     long long groups = forced > 0 ? 1LL * forced * num_seqs : work;
     long long cap = (forced > 0 ? 4LL : 1LL) * sm_count() * kCtasPerSm / pl.J;
@@ -1291,14 +1004,14 @@ static DecodePlan plan_decode(int num_seqs, int H, int G, int max_seq_len, int f
     pl.groups = static_cast<int>(groups);
     pl.rows = static_cast<size_t>((groups + num_seqs) * pl.J);
     pl.prefix_bytes = (static_cast<size_t>(num_seqs + 1) * sizeof(int32_t) + 255) / 256 * 256;
-    pl.bytes = pl.prefix_bytes + pl.rows * pl.ht * kQPerHead * (kHeadDim + 2) * sizeof(float);
+    pl.bytes = pl.prefix_bytes + pl.rows * kQPerHead * (kHeadDim + 2) * sizeof(float);
     return pl;
 }
 
 // ---- tensor maps of the cache ------------------------------------------------------------------
 //
-// The cache is described as a 2-D tensor of 8-byte elements (num_slots rows of total_bytes / 8): one
-// map per staged region, box = (region width, tokens per box), no swizzle.  cuTensorMapEncodeTiled is
+// The cache is described as a 2-D byte tensor (num_slots rows of total_bytes) with a box of 16 tokens
+// x 64 bytes (one index row per token) and 64-byte swizzle.  cuTensorMapEncodeTiled is
 // a driver entry point; it is looked up through the runtime so that the library does not link against
 // the driver.  Maps are remembered per (cache pointer, shape, box): a serving loop calls with the same
 // cache every step.
@@ -1344,12 +1057,12 @@ static bool encode_cache_map(CUtensorMap* map, const uint8_t* cache, int64_t num
         }
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(total_bytes / 8), static_cast<cuuint64_t>(num_slots)};
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(total_bytes), static_cast<cuuint64_t>(num_slots)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(total_bytes)};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes / 8), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t elem[2] = {1, 1};
-    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(cache), dims, strides, box, elem,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(cache), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     Entry& e = cache_maps[next];
@@ -1361,7 +1074,7 @@ static bool encode_cache_map(CUtensorMap* map, const uint8_t* cache, int64_t num
 }
 
 // Environment switches, read once per process:
-//   RQ_DECODE_NO_TMA=1            the issuer warp copies the rows with 4-byte cp.async (the path of odd block sizes)
+//   RQ_DECODE_NO_TMA=1            every thread loads its own rows (the path of odd block sizes)
 //   RQ_DECODE_NO_PDL=1            launch the merge without programmatic dependent launch
 //   RQ_DECODE_EQUAL_PIECES=1      no launch-layer weights
 //   RQ_DECODE_LAYER_WEIGHTS=a,b   weights of the launch layers (defaults below)
@@ -1393,68 +1106,30 @@ static const DecodeEnv& decode_env() {
     return env;
 }
 
-// Staging layout of a stage for this geometry: one region when the head tile is the whole slot payload,
-// else the four regions, each widened to 16-byte boundaries.
-static void plan_staging(DecodeParams& p) {
-    const int ttok = p.ttok;
-    // Row pitch of an index region: widened by 16-byte steps (the copy reads that much more of the slot)
-    // until consecutive tokens' 16-byte chunks fall into different shared-memory banks, i.e. the pitch
-    // in words is an odd multiple of 4 modulo 32.
-    auto conflict_free = [&](int w, int x_max) {
-        while (((w / 4) % 32) % 8 != 4 && x_max + w + 16 <= p.total_bytes) w += 16;
-        return w;
-    };
-    if (p.ht == p.H) {
-        p.n_regions = 1;
-        p.reg_w[0] = conflict_free((136 * p.H + 15) / 16 * 16, 0);
-        p.reg_base[0] = 0;
-        for (int r = 1; r < kRegions; ++r) { p.reg_w[r] = 0; p.reg_base[r] = 0; }
-        p.stage_bytes = ttok * p.reg_w[0];
-    } else {
-        p.n_regions = kRegions;
-        int base = 0;
-        for (int r = 0; r < kRegions; ++r) {
-            const int len = ((r & 1) ? 4 : kHalfDim) * p.ht;
-            int off_max = 0, x_max = 0;
-            for (int h0 = 0; h0 < p.H; h0 += p.ht) {
-                const RegionWindow rw = region_window(p.H, h0);
-                off_max = std::max(off_max, rw.start[r] - rw.x[r]);
-                x_max = std::max(x_max, rw.x[r]);
-            }
-            p.reg_w[r] = (off_max + len + 15) / 16 * 16;
-            if ((r & 1) == 0) p.reg_w[r] = conflict_free(p.reg_w[r], x_max);
-            p.reg_base[r] = base;
-            base += ttok * p.reg_w[r];
-        }
-        p.stage_bytes = base;
-    }
-    p.stages = std::min(kMaxStages, kRingBytes / p.stage_bytes);
-    p.v_aligned = p.H % 4 == 0 ? 1 : 0;
-}
-
 template <typename T, int KB, int VB>
-static int launch_decode(DecodeParams& p, int nh, cudaStream_t st) {
+static int launch_decode(DecodeParams& p, int nh, bool tma, cudaStream_t st) {
     if (!p.inline_plan) {
-        decode_plan_kernel<<<1, 1024, 0, st>>>(p.seq_lens, p.num_seqs, p.ttok, p.prefix);
+        decode_plan_kernel<<<1, 1024, 0, st>>>(p.seq_lens, p.num_seqs, kUTile, p.prefix);
         if (int e = check_cuda(cudaGetLastError(), "rq_decode plan launch")) return e;
     }
-    alignas(64) TmaMaps maps{};
-    const int64_t num_slots = p.num_blocks * p.block_size;
-    if (p.box_rows > 0) {
-        bool ok = true;
-        for (int r = 0; r < p.n_regions && ok; ++r)
-            ok = encode_cache_map(&maps.m[r], p.cache, num_slots, p.total_bytes, p.reg_w[r], p.box_rows);
-        if (!ok) p.box_rows = 0;                                           // no tensor maps: word copies
-    }
+    alignas(64) CUtensorMap map_idx{};
+    if (tma)
+        tma = encode_cache_map(&map_idx, p.cache, p.num_blocks * p.block_size, p.total_bytes, kHalfDim, kTokenBox);
     {
-        const size_t smem = sizeof(DecodeSmem) + 1024;                       // + hand alignment
-        const long long ctas = 1LL * p.groups * (p.H >> p.ht_shift) * p.head_groups;
+        const size_t smem = sizeof(UmmaSmem) + 512;                              // + hand alignment
+        const long long ctas = 1LL * p.groups * p.H * p.head_groups;
         auto launch = [&](auto kernel) -> int {
             if (int e = ensure_smem(kernel, smem)) return e;
-            kernel<<<static_cast<unsigned>(ctas), kDecodeThreads, smem, st>>>(p, maps);
+            kernel<<<static_cast<unsigned>(ctas), kUThreads, smem, st>>>(p, map_idx);
             return check_cuda(cudaGetLastError(), "rq_decode attention launch");
         };
-        if (int e = nh == 4 ? launch(decode_attn_kernel<T, KB, VB, 4>) : launch(decode_attn_kernel<T, KB, VB, 8>)) return e;
+        // rows by TMA when the geometry allows; V rows of 1 or 2 KV heads are not 16-byte aligned
+        const int mode = !tma ? 0 : (p.H % 4 == 0 ? 1 : 2);
+        int e = RQ_OK;
+        if (mode == 0) e = nh == 4 ? launch(decode_attn_kernel<T, KB, VB, 0, 4>) : launch(decode_attn_kernel<T, KB, VB, 0, 8>);
+        else if (mode == 1) e = nh == 4 ? launch(decode_attn_kernel<T, KB, VB, 1, 4>) : launch(decode_attn_kernel<T, KB, VB, 1, 8>);
+        else e = nh == 4 ? launch(decode_attn_kernel<T, KB, VB, 2, 4>) : launch(decode_attn_kernel<T, KB, VB, 2, 8>);
+        if (e) return e;
     }
 
     const long long warps = 1LL * p.num_seqs * p.Hq;
@@ -1477,11 +1152,11 @@ static int launch_decode(DecodeParams& p, int nh, cudaStream_t st) {
 }
 
 template <typename T>
-static int dispatch_bits(DecodeParams& p, int nh, int kb, int vb, cudaStream_t st) {
-    if (kb == 3 && vb == 3) return launch_decode<T, 3, 3>(p, nh, st);
-    if (kb == 4 && vb == 3) return launch_decode<T, 4, 3>(p, nh, st);
-    if (kb == 3 && vb == 4) return launch_decode<T, 3, 4>(p, nh, st);
-    return launch_decode<T, 4, 4>(p, nh, st);
+static int dispatch_bits(DecodeParams& p, int nh, bool tma, int kb, int vb, cudaStream_t st) {
+    if (kb == 3 && vb == 3) return launch_decode<T, 3, 3>(p, nh, tma, st);
+    if (kb == 4 && vb == 3) return launch_decode<T, 4, 3>(p, nh, tma, st);
+    if (kb == 3 && vb == 4) return launch_decode<T, 3, 4>(p, nh, tma, st);
+    return launch_decode<T, 4, 4>(p, nh, tma, st);
 }
 
 }  // namespace rq
@@ -1551,50 +1226,36 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
     p.seq_lens = seq_lens; p.cent_k = centroids_k; p.cent_v = centroids_v; p.rotation = rotation;
     p.qk_scale = sm_scale * 1.4426950408889634f;
     p.H = num_kv_heads; p.Hq = num_q_heads; p.G = G; p.head_groups = head_groups;
-    p.ht = pl.ht; p.ht_shift = pl.ht_shift;
-    p.ttok = kPairs / pl.ht;
-    p.ttok_shift = 7 - pl.ht_shift;
-    p.n_cols = std::max(16, pl.ht * 2 * pl.nh);
     p.prefix = static_cast<int32_t*>(workspace);
-    const size_t slots = pl.rows * pl.ht * kQPerHead;
+    const size_t slots = pl.rows * kQPerHead;
     p.ws_o = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.prefix_bytes);
     p.ws_m = p.ws_o + slots * kHeadDim;
     p.ws_l = p.ws_m + slots;
     p.num_seqs = num_seqs; p.groups = pl.groups;
     p.inline_plan = num_seqs <= kInlinePlanSeqs ? 1 : 0;
     p.bs_shift = bs_shift;
-    plan_staging(p);
-    // TMA boxes: power-of-two blocks of 8 tokens or more, slot numbers that fit a 32-bit coordinate
+    // TMA boxes of 16 tokens: power-of-two blocks of 16 tokens or more (a box never straddles a block),
+    // slot numbers that fit a 32-bit coordinate
     const DecodeEnv& env = decode_env();
-    p.box_rows = (!env.no_tma && bs_shift >= 3 && num_blocks * block_size <= INT32_MAX) ? std::min(block_size, p.ttok) : 0;
+    const bool tma = !env.no_tma && bs_shift >= 4 && num_blocks * block_size <= INT32_MAX;
     // Launch-layer weights: only when (nearly) every SM holds its full set of CTAs.  RQ_DECODE_LAYER_WEIGHTS
-    // overrides the defaults.
+    // overrides the defaults (measured: the CTAs launched first on an SM get the larger share of the
+    // issue slots while four run side by side).
     const int sms = sm_count();
     const long long ctas = 1LL * pl.groups * pl.J;
     p.layer_ctas = 0;
     p.num_layers = kCtasPerSm;
-    static const int kDefaultWeights[kMaxLayers] = {1024, 1024, 1024, 1024};
+    static const int kDefaultWeights[kMaxLayers] = {1290, 1090, 950, 766};
     for (int i = 0; i < kMaxLayers; ++i)
         p.layer_w[i] = env.n_weights > 0 ? env.weights[i < env.n_weights ? i : env.n_weights - 1] : kDefaultWeights[i];
     if (!env.equal_pieces && ctas > 1LL * (kCtasPerSm - 1) * sms) p.layer_ctas = sms;
     p.out = out; p.o_stride_seq = o_stride_seq; p.o_stride_head = o_stride_head;
-#ifdef RQ_DECODE_TRACE
-    p.trace = g_trace_buffer;
-#endif
 
     const int kb = n_centroids_k == 8 ? 3 : 4, vb = n_centroids_v == 8 ? 3 : 4;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == RQ_DTYPE_BF16) return dispatch_bits<__nv_bfloat16>(p, pl.nh, kb, vb, st);
-    return dispatch_bits<__half>(p, pl.nh, kb, vb, st);
+    if (dtype == RQ_DTYPE_BF16) return dispatch_bits<__nv_bfloat16>(p, pl.nh, tma, kb, vb, st);
+    return dispatch_bits<__half>(p, pl.nh, tma, kb, vb, st);
 }
-
-#ifdef RQ_DECODE_TRACE
-// Development builds only: device buffer of 3 x 5 x 64 x 16 clock values (see RQ_TRACE).
-extern "C" int rq_debug_set_trace(void* device_buffer) {
-    rq::g_trace_buffer = static_cast<unsigned long long*>(device_buffer);
-    return RQ_OK;
-}
-#endif
 
 // ---- decode with library-owned scratch ------------------------------------------------------
 //
