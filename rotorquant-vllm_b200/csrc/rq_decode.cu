@@ -153,7 +153,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar_addr, uint32_t bytes
 }
 
 // TMA: copy one 2-D box (inner coordinate x in elements, outer coordinate y) of the tensor described
-// by `map` into shared memory; completion is signalled on the mbarrier.  No multicast.
+// by `map` into shared memory; completion is signalled on the mbarrier.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
                                             uint32_t bar_addr) {
     asm volatile(

@@ -572,7 +572,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar_addr, uint32_t bytes
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
 }
 // Contiguous global -> shared copy of `bytes` (multiple of 16, both addresses 16-byte aligned),
-// completing on the mbarrier.  No multicast.
+// completing on the mbarrier.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar_addr) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar_addr) : "memory");
