@@ -26,6 +26,7 @@ namespace rq {
 constexpr int kCompressThreads = 256;                 // 16 rows per CTA
 constexpr int kRowsPerCta = kCompressThreads / 16;
 constexpr int kCompressGrid = 148 * 4;                // the grid walks the rows: at most 4 CTAs per SM
+constexpr int kRowBatch = 2;                          // rows fetched ahead per 16-thread group and step
 
 struct CompressParams {
     const void* src[2];          // key, value (or x, unused)
@@ -178,8 +179,8 @@ __device__ __forceinline__ uint32_t compress_chunk(const float (&x)[8], int j, f
 }
 
 // Store variant.  A fixed grid walks the rows: first all K rows (token-major, head-minor), then
-// all V rows, two rows per warp per step, the next rows' elements loaded while the current ones
-// are processed.  Every row's 16 threads write its 64 index bytes and its norm straight into the
+// all V rows, two rows per warp at a time, the elements of a step's rows all requested before the
+// first is processed.  Every row's 16 threads write its 64 index bytes and its norm straight into the
 // token's cache slot; the K row of head 0 also zeroes the slot's padding.
 template <typename T, int NB>
 __device__ __forceinline__ void store_rows(const CompressParams& p, int kv, const ThreadRotation& rot,
@@ -203,38 +204,44 @@ __device__ __forceinline__ void store_rows(const CompressParams& p, int kv, cons
         raw = load_raw8<T>(src + token * p.token_stride[kv] + static_cast<int64_t>(h) * p.head_stride[kv] + 8 * j);
         slot = __ldg(p.slot_mapping + token);
     };
-    Raw8<T> raw{}, nraw{};
-    int64_t slot = -1, nslot = -1;
-    // the two rows of a warp run in lock step (shuffles, __syncwarp): loop on the warp's first row
+    // the two rows of a warp run in lock step (shuffles, __syncwarp): loop on the warp's first row.
+    // A step fetches kRowBatch rows per thread group before it works on any of them, so that their
+    // load latencies overlap.
+    constexpr int B = kRowBatch;
     const uint32_t warp_first = first & ~1u;
-    if (warp_first < rows) fetch(first, raw, slot);
-    for (uint32_t wr = warp_first, r = first; wr < rows; wr += step, r += step) {
-        if (wr + step < rows) fetch(r + step, nraw, nslot);
-        float x[8];
-        unpack8<T>(raw, x);
-        float norm;
-        const uint32_t word = compress_chunk<NB>(x, j, sq_row, rot, bd, norm);
-        if (r < rows) {
-            uint32_t token, h;
-            locate(r, token, h);
-            if (slot >= 0 && slot < p.num_slots) {
-                uint8_t* dst = p.cache + slot * p.total_bytes;
-                *reinterpret_cast<uint32_t*>(dst + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim + 4 * j) = word;
-                if (j == 0) *reinterpret_cast<float*>(dst + (kv ? lay.v_norm : lay.k_norm) + 4 * h) = norm;
-                if (p.write_padding && kv == 0 && h == 0) {
-                    const int units = (lay.total - lay.payload_end) / 8;
-                    for (int u = j; u < units; u += 16)
-                        *reinterpret_cast<uint2*>(dst + lay.payload_end + 8 * u) = make_uint2(0u, 0u);
+    for (uint32_t wr = warp_first, r = first; wr < rows; wr += B * step, r += B * step) {
+        Raw8<T> raw[B];
+        int64_t slot[B];
+#pragma unroll
+        for (int b = 0; b < B; ++b)
+            if (wr + b * step < rows) fetch(r + b * step, raw[b], slot[b]);
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            if (wr + b * step >= rows) break;               // warp-uniform
+            const uint32_t rb = r + b * step;
+            float x[8];
+            unpack8<T>(raw[b], x);
+            float norm;
+            const uint32_t word = compress_chunk<NB>(x, j, sq_row, rot, bd, norm);
+            if (rb < rows) {
+                uint32_t token, h;
+                locate(rb, token, h);
+                if (slot[b] >= 0 && slot[b] < p.num_slots) {
+                    uint8_t* dst = p.cache + slot[b] * p.total_bytes;
+                    *reinterpret_cast<uint32_t*>(dst + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim + 4 * j) = word;
+                    if (j == 0) *reinterpret_cast<float*>(dst + (kv ? lay.v_norm : lay.k_norm) + 4 * h) = norm;
+                    if (p.write_padding && kv == 0 && h == 0) {
+                        const int units = (lay.total - lay.payload_end) / 8;
+                        for (int u = j; u < units; u += 16)
+                            *reinterpret_cast<uint2*>(dst + lay.payload_end + 8 * u) = make_uint2(0u, 0u);
+                    }
                 }
             }
         }
-        raw = nraw;
-        slot = nslot;
     }
 }
-
 template <typename T>
-__global__ void __launch_bounds__(kCompressThreads)
+__global__ void __launch_bounds__(kCompressThreads, 2)
 compress_store_kernel(const CompressParams p) {
     __shared__ __align__(16) float sq[kRowsPerCta][16 * 8];
     const int j = threadIdx.x & 15;
