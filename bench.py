@@ -49,7 +49,7 @@ UNIT = "tokens/s"
 # DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of the
 # attention kernel on the 32-sequence case) divided by the algorithmic bytes of the same launch;
 # traffic grows in proportion to the tokens streamed, so the ratio scales `roofline.traffic`.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 155.8e6 / 143.2e6
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 158.9e6 / 143.2e6
 COMPRESS_BYTES_PER_TOKEN = 5184          # 8 heads x 128 x 2 B x (K, V) read + 1088 B payload written
 MIN_TIMED_SECONDS = 0.5
 

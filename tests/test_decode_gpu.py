@@ -196,8 +196,8 @@ def test_bytes_past_the_end_of_a_sequence_are_ignored(dtype):
 
 
 def test_row_copy_staging_in_a_subprocess():
-    """RQ_DECODE_NO_TMA=1 (read once per process) stages the rows with 4-byte copies issued by the
-    issuer warp instead of TMA boxes, the path every unusual block size takes; RQ_DECODE_NO_PDL=1
+    """RQ_DECODE_NO_TMA=1 (read once per process) makes every thread load its own index rows instead
+    of staging them by TMA boxes, the path every unusual block size takes; RQ_DECODE_NO_PDL=1
     launches the merge without programmatic dependent launch and RQ_DECODE_EQUAL_PIECES=1 cuts the
     tile line into equal pieces.  Run the golden and edge cases under them in a child process."""
     import os
