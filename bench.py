@@ -438,26 +438,30 @@ class GpuJob:
                 "against": "oracle/rq_oracle.decode (reference decompress + SDPA), bound 2e-3 or one rounding flip"}
 
 
-def timed(fn, steps: int, device) -> float:
-    """Milliseconds for `steps` calls of fn, CUDA events on the current stream."""
+def timed(fn, steps: int, device, tail=None) -> float:
+    """Milliseconds for `steps` calls of fn, CUDA events on the current stream.  `tail`, when given, runs
+    after the last call and before the closing event (it makes the current stream wait for work that fn
+    put on another stream, so that the event covers it)."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(device)
     e0.record()
     for _ in range(steps):
         fn()
+    if tail is not None:
+        tail()
     e1.record()
     torch.cuda.synchronize(device)
     return e0.elapsed_time(e1)
 
 
-def timed_chunks(fn, steps: int, device, min_seconds: float = MIN_TIMED_SECONDS, max_chunks: int = 400):
+def timed_chunks(fn, steps: int, device, min_seconds: float = MIN_TIMED_SECONDS, max_chunks: int = 400, tail=None):
     """Time chunks of exactly `steps` calls until at least `min_seconds` have been measured;
     returns (median chunk in ms, number of chunks)."""
-    first = timed(fn, steps, device)
+    first = timed(fn, steps, device, tail)
     chunks = [first]
     want = min(max_chunks, max(1, math.ceil(min_seconds * 1e3 / max(first, 1e-3))))
     while len(chunks) < want:
-        chunks.append(timed(fn, steps, device))
+        chunks.append(timed(fn, steps, device, tail))
     return statistics.median(chunks), len(chunks)
 
 
@@ -523,16 +527,33 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     egraph = None if args.no_graph else capture(job.step_with_table_update, device, "the end-to-end step")
     erun = egraph.replay if egraph is not None else job.step_with_table_update
 
+    # The read-back runs on a second stream: PCIe is full duplex, so the output of step i travels to the
+    # host while the inputs of step i + 1 travel to the device.  Step i + 1 does not start computing before
+    # the read-back of step i has finished with the output buffer.
+    main = torch.cuda.current_stream(device)
+    reader = torch.cuda.Stream(device)
+    computed, read_back = torch.cuda.Event(), torch.cuda.Event()
+    read_back.record(main)
+
     def e2e_step():
         job.staging.copy_(host_in, non_blocking=True)
+        main.wait_event(read_back)
         erun()
-        host_out.copy_(result, non_blocking=True)
+        computed.record(main)
+        reader.wait_event(computed)
+        with torch.cuda.stream(reader):
+            host_out.copy_(result, non_blocking=True)
+            read_back.record(reader)
+
+    def e2e_tail():
+        main.wait_event(read_back)            # the closing event covers the last read-back
 
     for _ in range(3):
         e2e_step()
     barrier()
-    e2e_ms = timed_chunks(e2e_step, args.steps, device)[0]
+    e2e_ms = timed_chunks(e2e_step, args.steps, device, tail=e2e_tail)[0]
     barrier()
+    e2e_tail()
 
     t = torch.tensor([ms_chunk, e2e_ms, decode_eager_ms, decode_graph_ms or decode_eager_ms, compress_ms,
                       nogather_ms or 0.0], dtype=torch.float64, device=device)
@@ -818,7 +839,8 @@ def run_gpu_arm(args, w: syn.Workload) -> None:
             "e2e": {"value": seqs_per_step / (m["e2e_ms_per_step"] * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"],
                     "how": "one pinned staging buffer -> one H2D copy, graph replay (block-table delta + "
-                           "compress + decode), one D2H copy of the output"},
+                           "compress + decode), one D2H copy of the output on a second stream (it overlaps the "
+                           "next step's H2D copy; a step starts computing only after the previous read-back)"},
             "gpu_launches": job.launches_per_step * args.steps * m["chunks"],
             "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel (+ merge kernel)",
                          "achieved": achieved, "peak": peak["hbm_gbs"], "peak_kind": f"{peak['kind']} copy bandwidth",

@@ -75,6 +75,7 @@ struct DecodeParams {
     void* out;
     int64_t o_stride_seq, o_stride_head;
     int32_t* prefix;                       // [num_seqs + 1] exclusive prefix of tiles per sequence (workspace)
+    int2* seq_groups;                      // [num_seqs] first and last group whose piece holds tiles of the sequence
     int num_seqs;
     int groups;                            // pieces; CTA = (group, item), item = (KV head, head group)
     int inline_plan;                       // the attention CTAs compute the prefix sums themselves
@@ -420,6 +421,12 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         const int t_begin = static_cast<int>(x - pre);
         const int64_t reach = t_begin + (x_end - x);
         const int t_end = reach < n_s ? static_cast<int>(reach) : n_s;
+        // the merge reads which groups hold parts of a sequence: the CTAs of item 0 leave the first and the
+        // last one (the groups in between all do, their pieces being contiguous)
+        if (item == 0 && tid == 0) {
+            if (t_begin == 0) p.seq_groups[seq].x = static_cast<int>(group);
+            if (t_end == n_s) p.seq_groups[seq].y = static_cast<int>(group);
+        }
         const int kvh = item / p.head_groups, hg = item % p.head_groups;
         const int heads_here = min(kHeadsPerCta, p.G - hg * kHeadsPerCta);
         const int first_qh = kvh * p.G + hg * kHeadsPerCta;
@@ -863,13 +870,18 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num
 // part (group, sequence) of item j lives at row (group + sequence) * J + j, and inside the row the
 // query head sits in slot (query head within its group of 8).  Lanes
 // gather the running maxima and row sums of up to 32 parts at a time; then the warp sums the
-// weighted partial outputs.
+// weighted partial outputs.  Which groups those are was recorded per sequence by the attention CTAs.
 constexpr int kMergeWarps = 4;
 template <typename T>
 __global__ void __launch_bounds__(kMergeWarps * 32)
 decode_merge_kernel(const DecodeParams p) {
-    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
+    // the lane's 4x4 block of R does not depend on the attention launch: fetch it before waiting for that
+    float4 rr[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        rr[k] = __ldg(reinterpret_cast<const float4*>(p.rotation + (4 * lane + k) * kHeadDim + 4 * lane));
+    grid_dependency_wait();
     const int64_t wq = static_cast<int64_t>(blockIdx.x) * kMergeWarps + (threadIdx.x >> 5);
     if (wq >= static_cast<int64_t>(p.num_seqs) * p.Hq) return;
     const int seq = static_cast<int>(wq / p.Hq), qh = static_cast<int>(wq % p.Hq);
@@ -879,30 +891,29 @@ decode_merge_kernel(const DecodeParams p) {
     constexpr int slots = kQPerHead;
     const int slot = hl % kQPerHead;
     const int64_t a = p.prefix[seq], n = p.prefix[seq + 1] - a, total = p.prefix[p.num_seqs];
+    const int2 range = p.seq_groups[seq];
 
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float l_all = 0.0f;
     if (n > 0) {
-        // group holding tile t: the first g whose piece ends beyond t (32 candidates per round)
-        auto group_of = [&](int64_t t) -> int {
-            int lo = 0, hi = p.groups - 1;
-            while (lo < hi) {
-                const int step = (hi - lo + 30) / 31;                 // candidate 31 is always `hi`
-                const int c = min(lo + lane * step, hi);
-                const unsigned beyond = __ballot_sync(0xffffffffu, piece_begin(p, c + 1, total, J) > t);
-                const int f = __ffs(beyond) - 1;
-                const int new_hi = min(lo + f * step, hi);
-                lo = f == 0 ? lo : min(lo + (f - 1) * step, hi) + 1;
-                hi = new_hi;
-            }
-            return lo;
-        };
-        const int g_first = group_of(a), g_last = group_of(a + n - 1);
+        // first and last group with tiles of this sequence, as the attention CTAs recorded them (clamped: a
+        // CTA whose bounded wait expired may not have got there, and the output is NaN then anyway)
+        const int g_first = min(max(range.x, 0), p.groups - 1);
+        const int g_last = min(max(range.y, g_first), p.groups - 1);
+        // Groups whose piece is empty wrote nothing.  No piece is empty when the smallest weighted piece
+        // holds a tile, which is the normal case; only batches with fewer tiles than that check per group.
+        int min_w = 1024;
+        if (p.layer_ctas > 0) {
+            min_w = p.layer_w[0];
+            for (int i = 1; i < p.num_layers; ++i) min_w = min(min_w, p.layer_w[i]);
+        }
+        const bool dense = total * J * min_w >=
+                           weight_cum(static_cast<int64_t>(p.groups) * J, p.layer_ctas, p.num_layers, p.layer_w);
         float m_all = -INFINITY;
         for (int g0 = g_first; g0 <= g_last; g0 += 32) {             // normally one round
             const int gi = g0 + lane;
-            // groups whose piece is empty (only when there are more groups than tiles) wrote nothing
-            const bool live = gi <= g_last && piece_begin(p, gi, total, J) < piece_begin(p, gi + 1, total, J);
+            const bool live = gi <= g_last &&
+                              (dense || piece_begin(p, gi, total, J) < piece_begin(p, gi + 1, total, J));
             const int64_t r = ((static_cast<int64_t>(gi) + seq) * J + item) * slots + slot;
             const float m = live ? p.ws_m[r] : -INFINITY;
             const float l = live ? p.ws_l[r] : 0.0f;
@@ -937,12 +948,12 @@ decode_merge_kernel(const DecodeParams p) {
     float r[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const float4 rr = __ldg(reinterpret_cast<const float4*>(p.rotation + (4 * lane + k) * kHeadDim + 4 * lane));
         if (k == 0) {
-            r[0] = __fmul_rn(o[0], rr.x); r[1] = __fmul_rn(o[0], rr.y); r[2] = __fmul_rn(o[0], rr.z); r[3] = __fmul_rn(o[0], rr.w);
+            r[0] = __fmul_rn(o[0], rr[0].x); r[1] = __fmul_rn(o[0], rr[0].y);
+            r[2] = __fmul_rn(o[0], rr[0].z); r[3] = __fmul_rn(o[0], rr[0].w);
         } else {
-            r[0] = __fmaf_rn(o[k], rr.x, r[0]); r[1] = __fmaf_rn(o[k], rr.y, r[1]);
-            r[2] = __fmaf_rn(o[k], rr.z, r[2]); r[3] = __fmaf_rn(o[k], rr.w, r[3]);
+            r[0] = __fmaf_rn(o[k], rr[k].x, r[0]); r[1] = __fmaf_rn(o[k], rr[k].y, r[1]);
+            r[2] = __fmaf_rn(o[k], rr[k].z, r[2]); r[3] = __fmaf_rn(o[k], rr[k].w, r[3]);
         }
     }
     T* dst = static_cast<T*>(p.out) + seq * p.o_stride_seq + static_cast<int64_t>(qh) * p.o_stride_head + 4 * lane;
@@ -1003,7 +1014,9 @@ static DecodePlan plan_decode(int num_seqs, int H, int G, int max_seq_len, int f
     if (groups < 1) groups = 1;
     pl.groups = static_cast<int>(groups);
     pl.rows = static_cast<size_t>((groups + num_seqs) * pl.J);
-    pl.prefix_bytes = (static_cast<size_t>(num_seqs + 1) * sizeof(int32_t) + 255) / 256 * 256;
+    // tile prefix sums [num_seqs + 1] (int32, padded to 8 bytes), then the group range of every sequence (int2)
+    pl.prefix_bytes = ((static_cast<size_t>(num_seqs + 2) / 2 * 2) * sizeof(int32_t) +
+                       static_cast<size_t>(num_seqs) * sizeof(int2) + 255) / 256 * 256;
     pl.bytes = pl.prefix_bytes + pl.rows * kQPerHead * (kHeadDim + 2) * sizeof(float);
     return pl;
 }
@@ -1227,6 +1240,7 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
     p.qk_scale = sm_scale * 1.4426950408889634f;
     p.H = num_kv_heads; p.Hq = num_q_heads; p.G = G; p.head_groups = head_groups;
     p.prefix = static_cast<int32_t*>(workspace);
+    p.seq_groups = reinterpret_cast<int2*>(static_cast<int32_t*>(workspace) + (num_seqs + 2) / 2 * 2);
     const size_t slots = pl.rows * kQPerHead;
     p.ws_o = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.prefix_bytes);
     p.ws_m = p.ws_o + slots * kHeadDim;
