@@ -311,6 +311,7 @@ struct __align__(512) UmmaSmem {
     float red[4][kHeadsPerCta];              // cross-warp reductions
     int32_t prefix[kInlinePlanSeqs + 1];     // tile prefix sums when the CTA plans for itself
     int32_t scan[4];
+    int64_t piece[2];                        // this CTA's piece of the tile line
     uint64_t bar_s, bar_o;
     uint64_t bar_in[4];                      // per warp: "staged rows landed"
     uint32_t tmem_base;
@@ -330,8 +331,12 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     constexpr int NK = 1 << KB, NV = 1 << VB;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    // ---- tiles of every sequence as an exclusive prefix sum ----
+    // ---- tiles of every sequence as an exclusive prefix sum; this CTA's piece: CTA = (group, item) ----
+    const int J = p.H * p.head_groups;
+    const int64_t group = blockIdx.x / J;
+    const int item = static_cast<int>(blockIdx.x % J);
     const int32_t* prefix = p.prefix;
+    int64_t x, x_end;
     if (p.inline_plan) {                       // one sequence per thread, warp scan, four warp totals
         const int n = tid < p.num_seqs ? (max(__ldg(p.seq_lens + tid), 0) + kUTile - 1) / kUTile : 0;
         int incl = n;
@@ -346,22 +351,24 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         for (int w = 0; w < warp; ++w) before += sm.scan[w];
         if (tid == 0) sm.prefix[0] = 0;
         if (tid < p.num_seqs) sm.prefix[tid + 1] = before + incl;
+        // the two piece boundaries cost 64-bit divisions: two lanes compute them for the CTA
+        if (warp == 1 && lane < 2 && group < p.groups) {
+            const int64_t total = (sm.scan[0] + sm.scan[1]) + (sm.scan[2] + sm.scan[3]);
+            sm.piece[lane] = piece_begin(p, group + lane, total, J);
+        }
         __syncthreads();
         prefix = sm.prefix;
+        x = sm.piece[0];
+        x_end = sm.piece[1];
         if (blockIdx.x == 0)                   // the merge launch reads the prefix sums from the workspace
             for (int i = tid; i <= p.num_seqs; i += kUThreads) p.prefix[i] = sm.prefix[i];
+    } else if (group < p.groups) {
+        const int64_t total = prefix[p.num_seqs];
+        x = piece_begin(p, group, total, J);
+        x_end = piece_begin(p, group + 1, total, J);
     }
     if (tid == 0) grid_launch_dependents();    // the merge kernel may be scheduled; it waits for this grid's end
-
-    // ---- this CTA's piece: CTA = (group, item) ----
-    const int J = p.H * p.head_groups;
-    const int64_t total = prefix[p.num_seqs];
-    const int64_t group = blockIdx.x / J;
-    const int item = static_cast<int>(blockIdx.x % J);
-    if (group >= p.groups) return;
-    int64_t x = piece_begin(p, group, total, J);
-    const int64_t x_end = piece_begin(p, group + 1, total, J);
-    if (x >= x_end) return;
+    if (group >= p.groups || x >= x_end) return;
 
     if (tid == 0) {
         mbar_init(&sm.bar_s, 1);
