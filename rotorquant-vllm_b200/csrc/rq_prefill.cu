@@ -477,8 +477,56 @@ prefill_int8_kernel(const PrefillParams p) {
                 emit_chunk(r1, 1);
             }
         };
-        if (unmasked) softmax_half(std::false_type{});
-        else softmax_half(std::true_type{});
+        // After the first tile the reference maximum rarely moves, so the tile is first done in ONE pass
+        // against the current reference (scaled sums, their maximum and the probabilities together, nothing
+        // parked in TMEM, the raw sums left untouched); only when the maximum of some row of the warp does
+        // move is the tile redone by the two-pass code above.  Where the reference stays, both give the same bits.
+        auto softmax_one_pass = [&](auto masked_tag) -> bool {
+            constexpr bool kMasked = decltype(masked_tag)::value;
+            const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
+            float m_half = -INFINITY, l_try = l_run;
+#pragma unroll 1
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t r[32], pk[16];
+                tmem_ld32(lane_base + 64 * half + 32 * ch, r);
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const float4 ks = *reinterpret_cast<const float4*>(&k_scale[64 * half + 32 * ch + 4 * c4]);
+                    const float kk[4] = {ks.x, ks.y, ks.z, ks.w};
+                    float pr[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = 4 * c4 + e;
+                        const float sv = small_int_to_float(r[c]) * kk[e];
+                        const bool seen = !kMasked || 32 * ch + c <= limit;
+                        if (seen) m_half = fmaxf(m_half, sv);
+                        pr[e] = pf_ex2(fmaf(sv, row_factor, -m_use));
+                        if (!seen) pr[e] = 0.0f;
+                    }
+                    l_try += pr[0] + pr[1];
+                    l_try += pr[2] + pr[3];
+                    pk[2 * c4] = pf_pack<T>(pr[0], pr[1]);
+                    pk[2 * c4 + 1] = pf_pack<T>(pr[2], pr[3]);
+                }
+#pragma unroll
+                for (int kc = 0; kc < 4; ++kc)
+                    *reinterpret_cast<uint4*>(prow + (8 * half + 4 * ch + kc) * 128) =
+                        make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
+            }
+            sm.xch[half][row] = m_half;
+            pair_sync(quarter);
+            const float m_tile = fmaxf(m_half, sm.xch[half ^ 1][row]) * row_factor;
+            // both warps that share these rows see the same maxima, hence take the same decision
+            if (__any_sync(0xffffffffu, m_tile > m_run + 8.0f)) return false;
+            l_run = l_try;
+            return true;
+        };
+        bool done = false;
+        if (j > 0) done = unmasked ? softmax_one_pass(std::false_type{}) : softmax_one_pass(std::true_type{});
+        if (!done) {
+            if (unmasked) softmax_half(std::false_type{});
+            else softmax_half(std::true_type{});
+        }
         fence_async_proxy();
         tc_fence_before();
         if (__syncthreads_or(failed)) { failed = true; break; }      // uniform exit
@@ -913,8 +961,56 @@ prefill_attn_kernel(const PrefillParams p) {
                 emit_chunk(r1, 1);
             }
         };
-        if (unmasked) softmax_half(std::false_type{});
-        else softmax_half(std::true_type{});
+        // After the first tile the reference maximum rarely moves, so the tile is first done in ONE pass
+        // against the current reference (scaled sums, their maximum and the probabilities together, nothing
+        // parked in TMEM, the raw sums left untouched); only when the maximum of some row of the warp does
+        // move is the tile redone by the two-pass code above.  Where the reference stays, both give the same bits.
+        auto softmax_one_pass = [&](auto masked_tag) -> bool {
+            constexpr bool kMasked = decltype(masked_tag)::value;
+            const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
+            float m_half = -INFINITY, l_try = l_run;
+#pragma unroll 1
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t r[32], pk[16];
+                tmem_ld32(lane_base + 64 * half + 32 * ch, r);
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const float4 ks = *reinterpret_cast<const float4*>(&k_scale[64 * half + 32 * ch + 4 * c4]);
+                    const float kk[4] = {ks.x, ks.y, ks.z, ks.w};
+                    float pr[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = 4 * c4 + e;
+                        const float sv = small_int_to_float(r[c]) * kk[e];
+                        const bool seen = !kMasked || 32 * ch + c <= limit;
+                        if (seen) m_half = fmaxf(m_half, sv);
+                        pr[e] = pf_ex2(fmaf(sv, row_factor, -m_use));
+                        if (!seen) pr[e] = 0.0f;
+                    }
+                    l_try += pr[0] + pr[1];
+                    l_try += pr[2] + pr[3];
+                    pk[2 * c4] = pf_pack<T>(pr[0], pr[1]);
+                    pk[2 * c4 + 1] = pf_pack<T>(pr[2], pr[3]);
+                }
+#pragma unroll
+                for (int kc = 0; kc < 4; ++kc)
+                    *reinterpret_cast<uint4*>(prow + (8 * half + 4 * ch + kc) * 128) =
+                        make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
+            }
+            sm.xch[half][row] = m_half;
+            pair_sync(quarter);
+            const float m_tile = fmaxf(m_half, sm.xch[half ^ 1][row]) * row_factor;
+            // both warps that share these rows see the same maxima, hence take the same decision
+            if (__any_sync(0xffffffffu, m_tile > m_run + 8.0f)) return false;
+            l_run = l_try;
+            return true;
+        };
+        bool done = false;
+        if (j > 0) done = unmasked ? softmax_one_pass(std::false_type{}) : softmax_one_pass(std::true_type{});
+        if (!done) {
+            if (unmasked) softmax_half(std::false_type{});
+            else softmax_half(std::true_type{});
+        }
         failed |= !mbar_wait(&sm.bar_v, ph_v);                   // the V tile has landed
         ph_v ^= 1u;
         fence_async_proxy();
