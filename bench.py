@@ -66,6 +66,8 @@ def parse_args():
                     help="override the workload's number of sequences (small cases for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--gather", default="both", choices=["both", "peer", "nccl"],
+                    help="head-sharded step: exchange head outputs by peer stores, by NCCL all-gather, or time both")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip everything after the headline measurement (profiling runs)")
     ap.add_argument("--fused-prefill", action="store_true",
@@ -300,7 +302,8 @@ class GpuJob:
     heads (the layout tensor parallelism hands the layer); the head outputs are all-gathered.
     """
 
-    def __init__(self, w: syn.Workload, rank: int, world: int, device: torch.device, sharding: str | None = None):
+    def __init__(self, w: syn.Workload, rank: int, world: int, device: torch.device, sharding: str | None = None,
+                 gather_impl: str = "nccl"):
         from rotorquant_vllm import cuda as rq
 
         self.rq, self.w, self.dev, self.world = rq, w, device, world
@@ -375,7 +378,17 @@ class GpuJob:
         self.seq_lens.copy_(self.seq_lens_host.to(device))
         self.max_seq_len = int(self.seq_lens_host.max())
         self.gather = None
-        if self.sharding == "by KV head":
+        self.peer = None                # merge kernel stores into every GPU's buffer + arrive-and-wait kernel
+        self.gather_note = None
+        if self.sharding == "by KV head" and gather_impl == "peer" and world > 1:
+            try:
+                self.peer = parallel.PeerHeadGather(B, self.HQ, w.head_dim, w.dtype, device)
+            except Exception as exc:    # symmetric memory unavailable on this box: the NCCL form still works
+                self.gather_note = f"peer stores unavailable ({type(exc).__name__}: {exc}); NCCL all-gather used"
+                print(f"[bench] {self.gather_note}", file=sys.stderr)
+        if self.peer is not None:
+            self.out = self.peer.begin(0).local
+        elif self.sharding == "by KV head":
             self.gather = parallel.HeadGather(B, self.HQ, w.head_dim, w.dtype, device)
             self.out = self.gather.local
         else:
@@ -389,18 +402,35 @@ class GpuJob:
     def compress(self):
         self.rq.compress_and_store(self.new_k, self.new_v, self.cache, self.new_slots, self.R, self.kb, self.vb)
 
-    def decode_only(self):
+    def decode_only(self, peer_step=None):
         w = self.w
+        if self.peer is not None and peer_step is None:
+            peer_step = self.peer.begin(0)
         self.rq.fused_paged_rq_decode(self.q, self.cache, self.bt, self.seq_lens, self.kc, self.vc,
-                                      self.R, self.H, w.head_dim, w.block_size, out=self.out,
-                                      max_seq_len=self.max_seq_len, workspace=self.workspace)
+                                      self.R, self.H, w.head_dim, w.block_size,
+                                      out=self.out if peer_step is None else peer_step.local,
+                                      max_seq_len=self.max_seq_len, workspace=self.workspace,
+                                      peer_out_ptrs=None if peer_step is None else peer_step.peer_ptrs)
 
     def step(self):
-        """Device-resident step: compress-on-write, decode, and the head all-gather when sharded by head."""
+        """Device-resident step: compress-on-write, decode, and the exchange of head outputs when sharded by
+        head: either the merge kernel's peer stores + one arrive-and-wait kernel (two gathered buffers
+        alternate from step to step), or one in-place NCCL all-gather."""
         self.compress()
+        if self.peer is not None:
+            self.decode_only(self.peer.begin())
+            self.peer.finish()
+            return
         self.decode_only()
         if self.gather is not None:
             self.gather.gather()
+
+    @property
+    def gathered(self):
+        """The buffer an end-to-end step reads back."""
+        if self.peer is not None:
+            return self.peer.buffer[0]
+        return self.gather.buffer if self.gather is not None else self.out
 
     def step_with_table_update(self):
         """The step as the serving loop runs it: the block-table entries that changed are applied first."""
@@ -489,6 +519,15 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
         job.step()
     graph = None if args.no_graph else capture(job.step, device, "the step")
     runner = graph.replay if graph is not None else job.step
+    if graph is not None and job.peer is not None:
+        # the peer-store form alternates two gathered buffers: one graph per parity, replayed in turn
+        graph2 = capture(job.step, device, "the step (second gathered buffer)")
+        if graph2 is not None:
+            pair, turn_g = (graph, graph2), [0]
+
+            def runner():
+                pair[turn_g[0]].replay()
+                turn_g[0] ^= 1
     barrier()
     if sampler:
         sampler.start()
@@ -514,7 +553,7 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     compress_ms = timed(job.compress, min(args.steps, 200), device) / min(args.steps, 200)
     # the step without its collective, to price the gather
     nogather_ms = None
-    if job.gather is not None and world > 1:
+    if (job.gather is not None or job.peer is not None) and world > 1:
         g2 = None if args.no_graph else capture(lambda: (job.compress(), job.decode_only()), device, "the step without gather")
         fn = g2.replay if g2 is not None else (lambda: (job.compress(), job.decode_only()))
         nogather_ms = timed_chunks(fn, args.steps, device, 0.2)[0] / args.steps
@@ -522,7 +561,7 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
 
     # ---- end to end: ONE pinned host buffer -> device staging, table update + step, ONE read back ----
     host_in = job.staging.cpu().pin_memory()
-    result = job.gather.buffer if job.gather is not None else job.out
+    result = job.gathered
     host_out = torch.empty(result.shape, dtype=result.dtype).pin_memory()
     egraph = None if args.no_graph else capture(job.step_with_table_update, device, "the end-to-end step")
     erun = egraph.replay if egraph is not None else job.step_with_table_update
@@ -809,24 +848,68 @@ def measure_strong(args, rank: int, world: int, device, barrier) -> dict:
     w = syn.WORKLOADS["decode_70b_long"]
     if w.num_kv_heads % world:
         return {"unavailable": f"{w.num_kv_heads} KV heads do not split over {world} GPUs"}
-    job = GpuJob(w, rank, world, device, sharding="by KV head")
+    dist = torch.distributed
     sub = argparse.Namespace(**vars(args))
     sub.steps = max(10, min(args.steps, 100))
-    m = measure_job(job, sub, device, barrier, world)
     peak = measured_peaks()
-    alg = job.algorithmic_bytes()
-    gbs = alg / (m["decode_kernel_ms"] * 1e-3) / 1e9
-    res = {"workload": w.name, "sharding": "by KV head + one in-place NCCL all-gather of head outputs",
-           "kv_heads_per_gpu": job.H, "q_heads_per_gpu": job.HQ, "num_seqs": w.batch, "context": w.ctx_max,
-           "kernel_us": m["decode_kernel_ms"] * 1e3, "step_us": m["ms_per_step"] * 1e3,
-           "gather_us": (m["ms_per_step"] - m["nogather_ms"]) * 1e3 if m["nogather_ms"] else 0.0,
-           "e2e_step_us": m["e2e_ms_per_step"] * 1e3, "tokens_per_s": w.batch / (m["ms_per_step"] * 1e-3),
-           "algorithmic_bytes_per_gpu": alg, "achieved_gbs": gbs, "frac": gbs / peak["hbm_gbs"],
-           "cuda_graph": m["graph"]}
-    if rank == 0:
-        res["parity_check"] = job.parity_check(1)
-    del job
-    torch.cuda.empty_cache()
+    forms = ["peer", "nccl"] if world > 1 else ["nccl"]
+    if getattr(args, "gather", "both") in ("peer", "nccl") and world > 1:
+        forms = [args.gather]
+    out = {}
+    for form in forms:
+        job = GpuJob(w, rank, world, device, sharding="by KV head", gather_impl=form)
+        if form == "peer" and job.peer is None:
+            out["peer"] = {"unavailable": job.gather_note}
+            del job
+            torch.cuda.empty_cache()
+            continue
+        m = measure_job(job, sub, device, barrier, world)
+        alg = job.algorithmic_bytes()
+        gbs = alg / (m["decode_kernel_ms"] * 1e-3) / 1e9
+        how = ("merge kernel stores every output row into all GPUs' gathered buffers (peer memory over NVLink) + "
+               "one arrive-and-wait kernel" if form == "peer" else "one in-place NCCL all-gather of head outputs")
+        res = {"workload": w.name, "sharding": "by KV head; " + how,
+               "kv_heads_per_gpu": job.H, "q_heads_per_gpu": job.HQ, "num_seqs": w.batch, "context": w.ctx_max,
+               "kernel_us": m["decode_kernel_ms"] * 1e3, "step_us": m["ms_per_step"] * 1e3,
+               "gather_us": (m["ms_per_step"] - m["nogather_ms"]) * 1e3 if m["nogather_ms"] else 0.0,
+               "e2e_step_us": m["e2e_ms_per_step"] * 1e3, "tokens_per_s": w.batch / (m["ms_per_step"] * 1e-3),
+               "algorithmic_bytes_per_gpu": alg, "achieved_gbs": gbs, "frac": gbs / peak["hbm_gbs"],
+               "cuda_graph": m["graph"]}
+        if world > 1:
+            # the gathered buffer of one more step against an NCCL all-gather of the local head outputs
+            barrier()
+            if job.peer is not None:
+                par = job.peer.parity
+                job.step()
+                torch.cuda.synchronize(device)
+                got, local = job.peer.buffer[par], job.peer.buffer[par, rank]
+            else:
+                job.step()
+                torch.cuda.synchronize(device)
+                got, local = job.gather.buffer, job.gather.local
+            ref = torch.empty_like(got)
+            dist.all_gather_into_tensor(ref.view(-1, *local.shape[1:]), local.contiguous())
+            ok = torch.tensor([1 if torch.equal(got, ref) else 0], device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            res["gathered_equals_all_gather_on_every_rank"] = bool(ok.item())
+            if job.peer is not None:
+                bad = torch.tensor([1 if job.peer.wait_expired() else 0], device=device)
+                dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+                res["a_bounded_wait_expired"] = bool(bad.item())
+        if rank == 0:
+            res["parity_check"] = job.parity_check(1)
+        out[form] = res
+        del job
+        torch.cuda.empty_cache()
+        barrier()
+    head = out.get("peer") if "step_us" in out.get("peer", {}) else out.get("nccl")
+    res = dict(head) if head else {"unavailable": "no form of the head-sharded step ran"}
+    if "nccl" in out and head is not out.get("nccl"):
+        res["nccl_all_gather_form"] = {k: out["nccl"][k] for k in ("step_us", "gather_us", "kernel_us", "tokens_per_s",
+                                                                    "gathered_equals_all_gather_on_every_rank")
+                                       if k in out["nccl"]}
+    if "peer" in out and "unavailable" in out["peer"]:
+        res["peer_store_form"] = out["peer"]
     return res
 
 

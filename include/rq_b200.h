@@ -138,6 +138,40 @@ int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq, int64_t
               size_t workspace_bytes, int num_splits, void* stream);
 
 /*
+ * Head-sharded decode for tensor parallelism: rq_decode on this GPU's KV heads whose merge kernel stores
+ * every output row into `num_peers` buffers (host array of device pointers; one per GPU of the group, the
+ * calling GPU's own among them; peer buffers are memory of other GPUs mapped into this process, e.g.
+ * symmetric memory), at the offsets `o_stride_*` describe.  Each pointer addresses the place of THIS GPU's
+ * heads inside that GPU's gathered buffer.  Plain stores over NVLink; nothing else differs from rq_decode
+ * (same workspace, same bounded waits).  Follow it with rq_peer_barrier on every GPU of the group, and
+ * alternate between two gathered buffers from step to step: a GPU may be one step ahead of a peer that
+ * still reads the previous step's buffer.
+ * No counterpart in the reference; replaces "decode + all-gather of the attention outputs" of a tensor-
+ * parallel layer (vLLM runs that collective itself after the backend returns).
+ */
+int rq_decode_sharded(const void* q, int dtype, int64_t q_stride_seq, int64_t q_stride_head,
+                      int64_t o_stride_seq, int64_t o_stride_head, int num_seqs, int num_q_heads,
+                      int num_kv_heads, int head_dim, const uint8_t* kv_cache, int64_t num_blocks,
+                      int block_size, int total_bytes, const int32_t* block_table,
+                      int64_t block_table_stride, const int32_t* seq_lens, const float* centroids_k,
+                      int n_centroids_k, const float* centroids_v, int n_centroids_v,
+                      const float* rotation, float sm_scale, int max_seq_len, void* workspace,
+                      size_t workspace_bytes, int num_splits, void* const* peer_out, int num_peers,
+                      void* stream);
+
+/*
+ * Arrive-and-wait of the GPUs of a group, enqueued on `stream` after rq_decode_sharded: one warp writes this
+ * GPU's step number into slot `rank` of every GPU's flag array and waits until all `world` slots of its own
+ * array have reached it.  `peer_flags` is a host array of `world` device pointers (uint64[world] each, zeroed
+ * once, this GPU's own array at index `rank`), `state` two uint64 on this GPU, zeroed once: state[0] counts
+ * the steps, state[1] becomes 1 when a wait ran out.  The wait is bounded by `limit_cycles` SM clocks (0 =
+ * about one second); on expiry the kernel records it and returns, it never traps.  Step numbers live on the
+ * device, so the call can be captured in a CUDA graph.  No counterpart in the reference.
+ */
+int rq_peer_barrier(void* const* peer_flags, int world, int rank, void* state, long long limit_cycles,
+                    void* stream);
+
+/*
  * rq_decode for callers that cannot supply a workspace.  It has no counterpart in the reference.
  *
  * Who needs it: a caller that is unable to obtain device memory of its own when the decode call

@@ -15,7 +15,7 @@ import sys
 CSRC = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.join(os.path.dirname(CSRC), "rotorquant_vllm")
 LIB = os.path.join(PKG, "librq_b200.so")
-SOURCES = ["rq_api.cu", "rq_compress.cu", "rq_decode.cu", "rq_prefill.cu", "rq_probe.cu"]
+SOURCES = ["rq_api.cu", "rq_compress.cu", "rq_decode.cu", "rq_peer.cu", "rq_prefill.cu", "rq_probe.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

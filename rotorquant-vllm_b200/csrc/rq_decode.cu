@@ -52,6 +52,7 @@ constexpr int kTokenBox = 16;                // tokens per TMA box (never stradd
 constexpr int kInlinePlanSeqs = 128;         // up to this many sequences the CTAs scan seq_lens themselves
 constexpr int kMaxLayers = 4;                // launch layers with their own piece weight
 constexpr int kCtasPerSm = 4;
+constexpr int kMaxPeers = 8;                 // GPUs of one NVLink domain that a sharded decode writes to
 
 struct DecodeParams {
     const void* q;
@@ -74,6 +75,10 @@ struct DecodeParams {
     float* ws_l;
     void* out;
     int64_t o_stride_seq, o_stride_head;
+    // head-sharded decode: the merge writes every output row into the same place of each GPU's gathered
+    // buffer (plain stores over NVLink into peer memory; the local GPU's buffer is one of the entries)
+    void* peer_out[kMaxPeers];
+    int num_peers;                         // 0: write `out` only
     int32_t* prefix;                       // [num_seqs + 1] exclusive prefix of tiles per sequence (workspace)
     int2* seq_groups;                      // [num_seqs] first and last group whose piece holds tiles of the sequence
     int num_seqs;
@@ -963,13 +968,22 @@ decode_merge_kernel(const DecodeParams p) {
             r[2] = __fmaf_rn(o[k], rr[k].z, r[2]); r[3] = __fmaf_rn(o[k], rr[k].w, r[3]);
         }
     }
-    T* dst = static_cast<T*>(p.out) + seq * p.o_stride_seq + static_cast<int64_t>(qh) * p.o_stride_head + 4 * lane;
+    const int64_t offset = seq * p.o_stride_seq + static_cast<int64_t>(qh) * p.o_stride_head + 4 * lane;
     const uint2 packed = make_uint2(pack_pair<T>(r[0], r[1]), pack_pair<T>(r[2], r[3]));
-    if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
-        *reinterpret_cast<uint2*>(dst) = packed;
-    } else {
+    auto store = [&](void* base) {
+        T* dst = static_cast<T*>(base) + offset;
+        if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+            *reinterpret_cast<uint2*>(dst) = packed;
+        } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) store_rounded(dst + j, r[j]);
+            for (int j = 0; j < 4; ++j) store_rounded(dst + j, r[j]);
+        }
+    };
+    if (p.num_peers == 0) {
+        store(p.out);
+    } else {
+        for (int g = 0; g < p.num_peers; ++g) store(p.peer_out[g]);
+        __threadfence_system();            // the peers' copies are on their way before this grid ends
     }
 }
 
@@ -1190,15 +1204,19 @@ extern "C" size_t rq_decode_workspace_bytes(int num_seqs, int num_q_heads, int n
     return plan_decode(num_seqs, num_kv_heads, num_q_heads / num_kv_heads, max_seq_len, num_splits).bytes;
 }
 
-extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq,
-                         int64_t q_stride_head, int64_t o_stride_seq, int64_t o_stride_head,
-                         int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
-                         const uint8_t* kv_cache, int64_t num_blocks, int block_size,
-                         int total_bytes, const int32_t* block_table, int64_t block_table_stride,
-                         const int32_t* seq_lens, const float* centroids_k, int n_centroids_k,
-                         const float* centroids_v, int n_centroids_v, const float* rotation,
-                         float sm_scale, int max_seq_len, void* workspace, size_t workspace_bytes,
-                         int num_splits, void* stream) {
+static int decode_impl(const void* q, void* out, int dtype, int64_t q_stride_seq,
+                       int64_t q_stride_head, int64_t o_stride_seq, int64_t o_stride_head,
+                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                       const uint8_t* kv_cache, int64_t num_blocks, int block_size,
+                       int total_bytes, const int32_t* block_table, int64_t block_table_stride,
+                       const int32_t* seq_lens, const float* centroids_k, int n_centroids_k,
+                       const float* centroids_v, int n_centroids_v, const float* rotation,
+                       float sm_scale, int max_seq_len, void* workspace, size_t workspace_bytes,
+                       int num_splits, void* const* peer_out, int num_peers, void* stream) {
+    if (num_peers < 0 || num_peers > kMaxPeers || (num_peers > 0 && peer_out == nullptr))
+        return fail(RQ_ERR_INVALID_ARG, "rq_decode: %d peer outputs (at most %d)", num_peers, kMaxPeers);
+    for (int g = 0; g < num_peers; ++g)
+        if (peer_out[g] == nullptr) return fail(RQ_ERR_INVALID_ARG, "rq_decode: null peer output %d", g);
     if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_blocks < 0 || block_size <= 0 ||
         max_seq_len < 0 || num_splits < 0)
         return fail(RQ_ERR_INVALID_ARG, "rq_decode: negative or zero size");
@@ -1271,11 +1289,50 @@ extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_s
         p.layer_w[i] = env.n_weights > 0 ? env.weights[i < env.n_weights ? i : env.n_weights - 1] : kDefaultWeights[i];
     if (!env.equal_pieces && ctas > 1LL * (kCtasPerSm - 1) * sms) p.layer_ctas = sms;
     p.out = out; p.o_stride_seq = o_stride_seq; p.o_stride_head = o_stride_head;
+    p.num_peers = num_peers;
+    for (int g = 0; g < num_peers; ++g) p.peer_out[g] = peer_out[g];
 
     const int kb = n_centroids_k == 8 ? 3 : 4, vb = n_centroids_v == 8 ? 3 : 4;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == RQ_DTYPE_BF16) return dispatch_bits<__nv_bfloat16>(p, pl.nh, tma, kb, vb, st);
     return dispatch_bits<__half>(p, pl.nh, tma, kb, vb, st);
+}
+
+extern "C" int rq_decode(const void* q, void* out, int dtype, int64_t q_stride_seq,
+                         int64_t q_stride_head, int64_t o_stride_seq, int64_t o_stride_head,
+                         int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                         const uint8_t* kv_cache, int64_t num_blocks, int block_size,
+                         int total_bytes, const int32_t* block_table, int64_t block_table_stride,
+                         const int32_t* seq_lens, const float* centroids_k, int n_centroids_k,
+                         const float* centroids_v, int n_centroids_v, const float* rotation,
+                         float sm_scale, int max_seq_len, void* workspace, size_t workspace_bytes,
+                         int num_splits, void* stream) {
+    return decode_impl(q, out, dtype, q_stride_seq, q_stride_head, o_stride_seq, o_stride_head, num_seqs,
+                       num_q_heads, num_kv_heads, head_dim, kv_cache, num_blocks, block_size, total_bytes,
+                       block_table, block_table_stride, seq_lens, centroids_k, n_centroids_k, centroids_v,
+                       n_centroids_v, rotation, sm_scale, max_seq_len, workspace, workspace_bytes, num_splits,
+                       nullptr, 0, stream);
+}
+
+// Head-sharded decode: rq_decode whose merge kernel writes every output row into `num_peers` buffers, one
+// per GPU of the tensor-parallel group (the calling GPU's own gathered buffer among them), at the same
+// offsets as `out`.  Followed by rq_peer_barrier it replaces "decode + all-gather of the head outputs".
+extern "C" int rq_decode_sharded(const void* q, int dtype, int64_t q_stride_seq, int64_t q_stride_head,
+                                 int64_t o_stride_seq, int64_t o_stride_head, int num_seqs, int num_q_heads,
+                                 int num_kv_heads, int head_dim, const uint8_t* kv_cache, int64_t num_blocks,
+                                 int block_size, int total_bytes, const int32_t* block_table,
+                                 int64_t block_table_stride, const int32_t* seq_lens, const float* centroids_k,
+                                 int n_centroids_k, const float* centroids_v, int n_centroids_v,
+                                 const float* rotation, float sm_scale, int max_seq_len, void* workspace,
+                                 size_t workspace_bytes, int num_splits, void* const* peer_out, int num_peers,
+                                 void* stream) {
+    if (num_peers <= 0 || peer_out == nullptr)
+        return fail(RQ_ERR_INVALID_ARG, "rq_decode_sharded: at least one output buffer is needed");
+    return decode_impl(q, peer_out[0], dtype, q_stride_seq, q_stride_head, o_stride_seq, o_stride_head, num_seqs,
+                       num_q_heads, num_kv_heads, head_dim, kv_cache, num_blocks, block_size, total_bytes,
+                       block_table, block_table_stride, seq_lens, centroids_k, n_centroids_k, centroids_v,
+                       n_centroids_v, rotation, sm_scale, max_seq_len, workspace, workspace_bytes, num_splits,
+                       peer_out, num_peers, stream);
 }
 
 // ---- decode with library-owned scratch ------------------------------------------------------

@@ -35,6 +35,9 @@ _SIGNATURES = {
     "rq_decode_workspace_bytes": (_Z, [_I, _I, _I, _I, _I, _I]),
     "rq_decode": (_I, [_P, _P, _I, _L, _L, _L, _L, _I, _I, _I, _I, _P, _L, _I, _I, _P, _L, _P, _P,
                        _I, _P, _I, _P, _F, _I, _P, _Z, _I, _P]),
+    "rq_decode_sharded": (_I, [_P, _I, _L, _L, _L, _L, _I, _I, _I, _I, _P, _L, _I, _I, _P, _L, _P, _P,
+                               _I, _P, _I, _P, _F, _I, _P, _Z, _I, C.POINTER(C.c_void_p), _I, _P]),
+    "rq_peer_barrier": (_I, [C.POINTER(C.c_void_p), _I, _I, _P, C.c_longlong, _P]),
     "rq_decode_static_scratch": (_I, [_P, _P, _I, _L, _L, _L, _L, _I, _I, _I, _I, _P, _L, _I, _I, _P, _L, _P,
                                       _P, _I, _P, _I, _P, _F, _I, _I, _P]),
     "rq_prefill_int8": (_I, [_P, _P, _I, _L, _L, _L, _L, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P,

@@ -64,6 +64,7 @@ def fused_paged_rq_decode(
     max_seq_len: int | None = None,
     workspace: torch.Tensor | None = None,
     num_splits: int = 0,
+    peer_out_ptrs: list[int] | None = None,
 ) -> torch.Tensor:
     """Decode attention of one query token per sequence over the compressed paged cache.
 
@@ -74,6 +75,11 @@ def fused_paged_rq_decode(
 
     ``max_seq_len`` (host integer bounding ``seq_lens``; default: table width x block size) only
     sizes the launch; nothing is read back from the device, so the call can be graph-captured.
+
+    ``peer_out_ptrs`` (head-sharded decode): device addresses, one per GPU of the tensor-parallel
+    group, of the place of THIS GPU's heads inside each GPU's gathered output buffer, laid out like
+    ``out`` (which must be this GPU's own entry).  The merge kernel then stores every output row into
+    all of them; see :class:`rotorquant_vllm.parallel.PeerHeadGather`.
     """
     num_seqs, hq, d = q.shape
     assert d == head_dim, f"D={d} != head_dim={head_dim}"
@@ -105,6 +111,22 @@ def fused_paged_rq_decode(
     seq_lens = seq_lens.contiguous()
     need = decode_workspace_bytes(num_seqs, hq, num_kv_heads, head_dim, max_seq_len, num_splits)
     ws = workspace if workspace is not None else _workspace(dev, need)
+    if peer_out_ptrs:
+        if out is None or int(out.data_ptr()) not in [int(p) for p in peer_out_ptrs]:
+            raise ValueError("peer_out_ptrs needs `out`, and out's own address among the pointers")
+        import ctypes
+
+        ptrs = (ctypes.c_void_p * len(peer_out_ptrs))(*[int(p) for p in peer_out_ptrs])
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().rq_decode_sharded(
+                q.data_ptr(), _lib.dtype_code(q.dtype), q.stride(0), q.stride(1),
+                result.stride(0), result.stride(1), num_seqs, hq, num_kv_heads, head_dim,
+                kv_cache.data_ptr(), kv_cache.shape[0], block_size, kv_cache.shape[2],
+                block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
+                ck.data_ptr(), ck.numel(), cv.data_ptr(), cv.numel(), rotation.data_ptr(),
+                float(sm_scale), int(max_seq_len), ws.data_ptr(), ws.numel() * ws.element_size(),
+                int(num_splits), ptrs, len(peer_out_ptrs), _lib.stream_ptr(dev)))
+        return result
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().rq_decode(
             q.data_ptr(), result.data_ptr(), _lib.dtype_code(q.dtype), q.stride(0), q.stride(1),

@@ -95,3 +95,80 @@ def gather_head_outputs(local_out: torch.Tensor, group=None) -> torch.Tensor:
     gathered = torch.empty(world, *local_out.shape, dtype=local_out.dtype, device=local_out.device)
     dist.all_gather_into_tensor(gathered.view(-1, *local_out.shape[1:]), local_out, group=group)
     return gathered.permute(1, 0, 2, 3).reshape(local_out.shape[0], world * local_out.shape[1], local_out.shape[2])
+
+
+class PeerHeadGather:
+    """The head-sharded path without a collective launch: the decode's merge kernel stores every output
+    row into ALL GPUs' gathered buffers (plain stores into peer memory over NVLink), and one small
+    arrive-and-wait kernel tells each GPU that its peers' rows have landed.
+
+    The gathered buffers live in symmetric memory (``torch.distributed._symmetric_memory``), which maps
+    every rank's allocation into every process.  ``buffer`` is ``(2, world, num_seqs, H_Q/world, D)``:
+    two gathered outputs that alternate from step to step, because a GPU that has passed the wait of
+    step ``i`` may already store step ``i + 1`` into a peer that still reads step ``i``.  Per step:
+
+        g = gather.begin()                                   # picks the buffer of this step
+        fused_paged_rq_decode(..., out=g.local, peer_out_ptrs=g.peer_ptrs)
+        result = gather.finish()                             # rq_peer_barrier; (num_seqs, world, H_Q/world, D)
+
+    All of it runs on the current stream; nothing allocates or synchronises with the host, and both
+    calls can sit in a captured CUDA graph (one graph per parity).  The wait is bounded (about a second
+    of SM clocks); :meth:`wait_expired` reads back whether one ever ran out.
+    """
+
+    class _Step:
+        __slots__ = ("local", "peer_ptrs", "result")
+
+    def __init__(self, num_seqs: int, heads_per_rank: int, head_dim: int, dtype: torch.dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+
+        self._lib = _lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        shape = (2, self.world, num_seqs, heads_per_rank, head_dim)
+        self.buffer = symm.empty(shape, dtype=dtype, device=self.device)
+        self.buffer.zero_()
+        self._buf_handle = symm.rendezvous(self.buffer, self.group)
+        self.flags = symm.empty((16,), dtype=torch.int64, device=self.device)
+        self.flags.zero_()
+        self._flag_handle = symm.rendezvous(self.flags, self.group)
+        self.state = torch.zeros(2, dtype=torch.int64, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)                                   # every rank's flags are zero before anyone arrives
+        esz = self.buffer.element_size()
+        slice_elems = num_seqs * heads_per_rank * head_dim
+        self._steps = []
+        for parity in range(2):
+            st = PeerHeadGather._Step()
+            st.local = self.buffer[parity, self.rank]
+            offset = ((parity * self.world + self.rank) * slice_elems) * esz
+            st.peer_ptrs = [int(base) + offset for base in self._buf_handle.buffer_ptrs]
+            st.result = self.buffer[parity].permute(1, 0, 2, 3)
+            self._steps.append(st)
+        assert st.peer_ptrs[self.rank] == st.local.data_ptr()
+        import ctypes
+
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self._flag_handle.buffer_ptrs])
+        self.parity = 0
+
+    def begin(self, parity: int | None = None) -> "PeerHeadGather._Step":
+        if parity is not None:
+            self.parity = parity & 1
+        return self._steps[self.parity]
+
+    def finish(self, limit_cycles: int = 0) -> torch.Tensor:
+        step = self._steps[self.parity]
+        with torch.cuda.device(self.device):
+            self._lib.check(self._lib.lib().rq_peer_barrier(
+                self._flag_ptrs, self.world, self.rank, self.state.data_ptr(), int(limit_cycles),
+                self._lib.stream_ptr(self.device)))
+        self.parity ^= 1
+        return step.result
+
+    def wait_expired(self) -> bool:
+        """Host read-back (synchronises): True when a bounded wait of this GPU has ever run out."""
+        return bool(int(self.state[1].item()))
