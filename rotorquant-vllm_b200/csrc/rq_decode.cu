@@ -982,8 +982,9 @@ decode_merge_kernel(const DecodeParams p) {
     if (p.num_peers == 0) {
         store(p.out);
     } else {
+        // No fence here: the arrive-and-wait kernel that announces these rows is a later launch on the same
+        // stream, and a grid has ended only when all its stores, peer memory included, have been performed.
         for (int g = 0; g < p.num_peers; ++g) store(p.peer_out[g]);
-        __threadfence_system();            // the peers' copies are on their way before this grid ends
     }
 }
 
