@@ -484,12 +484,16 @@ def timed(fn, steps: int, device, tail=None) -> float:
     return e0.elapsed_time(e1)
 
 
-def timed_chunks(fn, steps: int, device, min_seconds: float = MIN_TIMED_SECONDS, max_chunks: int = 400, tail=None):
+def timed_chunks(fn, steps: int, device, min_seconds: float = MIN_TIMED_SECONDS, max_chunks: int = 400, tail=None,
+                 agree=None):
     """Time chunks of exactly `steps` calls until at least `min_seconds` have been measured;
-    returns (median chunk in ms, number of chunks)."""
+    returns (median chunk in ms, number of chunks).  `agree(n) -> n` makes the ranks of a job settle on
+    one chunk count: every rank must run a step that holds an exchange the same number of times."""
     first = timed(fn, steps, device, tail)
     chunks = [first]
     want = min(max_chunks, max(1, math.ceil(min_seconds * 1e3 / max(first, 1e-3))))
+    if agree is not None:
+        want = agree(want)
     while len(chunks) < want:
         chunks.append(timed(fn, steps, device, tail))
     return statistics.median(chunks), len(chunks)
@@ -531,7 +535,14 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     barrier()
     if sampler:
         sampler.start()
-    ms_chunk, n_chunks = timed_chunks(runner, args.steps, device)
+    def agree(n: int) -> int:                   # the largest count any rank wants
+        if world == 1:
+            return n
+        t = torch.tensor([n], dtype=torch.int64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return int(t.item())
+
+    ms_chunk, n_chunks = timed_chunks(runner, args.steps, device, agree=agree)
     barrier()
 
     # ---- the dominant kernel alone (attention + merge), same inputs: in a graph, and launched one by one ----
@@ -539,7 +550,7 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     dgraph = None if args.no_graph else capture(job.decode_only, device, "the decode launches")
     decode_graph_ms = None
     if dgraph is not None:
-        decode_graph_ms = timed_chunks(dgraph.replay, args.steps, device, 0.2)[0] / args.steps
+        decode_graph_ms = timed_chunks(dgraph.replay, args.steps, device, 0.2, agree=agree)[0] / args.steps
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in range(min(args.steps, 200))]
     torch.cuda.synchronize(device)
@@ -556,7 +567,7 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     if (job.gather is not None or job.peer is not None) and world > 1:
         g2 = None if args.no_graph else capture(lambda: (job.compress(), job.decode_only()), device, "the step without gather")
         fn = g2.replay if g2 is not None else (lambda: (job.compress(), job.decode_only()))
-        nogather_ms = timed_chunks(fn, args.steps, device, 0.2)[0] / args.steps
+        nogather_ms = timed_chunks(fn, args.steps, device, 0.2, agree=agree)[0] / args.steps
     clocks = sampler.stop() if sampler else None
 
     # ---- end to end: ONE pinned host buffer -> device staging, table update + step, ONE read back ----
@@ -574,7 +585,7 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
 
     for _ in range(3):
         e2e_serial_step()
-    e2e_serial_ms = timed_chunks(e2e_serial_step, args.steps, device, 0.2)[0]
+    e2e_serial_ms = timed_chunks(e2e_serial_step, args.steps, device, 0.2, agree=agree)[0]
 
     # Pipelined form: PCIe is full duplex and the copy engines run beside the SMs, so the inputs of step
     # i + 1 are uploaded (into one of two landing buffers, on an upload stream) and the output of step i - 1
@@ -617,7 +628,7 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     for _ in range(4):
         e2e_step()
     barrier()
-    e2e_ms = timed_chunks(e2e_step, args.steps, device, tail=e2e_tail)[0]
+    e2e_ms = timed_chunks(e2e_step, args.steps, device, tail=e2e_tail, agree=agree)[0]
     barrier()
     e2e_tail()
     torch.cuda.synchronize(device)
