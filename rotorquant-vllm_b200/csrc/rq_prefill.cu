@@ -477,14 +477,14 @@ prefill_int8_kernel(const PrefillParams p) {
                 emit_chunk(r1, 1);
             }
         };
-        // After the first tile the reference maximum rarely moves, so the tile is first done in ONE pass
-        // against the current reference (scaled sums, their maximum and the probabilities together, nothing
-        // parked in TMEM, the raw sums left untouched); only when the maximum of some row of the warp does
-        // move is the tile redone by the two-pass code above.  Where the reference stays, both give the same bits.
+        // After the first tile the reference maximum rarely has to move, so the tile is first done in ONE
+        // pass against the current reference (scaled sums and probabilities together, nothing parked in TMEM,
+        // the raw sums left untouched); only when some row of the warp has outgrown its reference is the
+        // tile redone by the two-pass code above, which also finds the new maximum.
         auto softmax_one_pass = [&](auto masked_tag) -> bool {
             constexpr bool kMasked = decltype(masked_tag)::value;
             const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
-            float m_half = -INFINITY, l_try = l_run;
+            float l_try = l_run;
 #pragma unroll 1
             for (int ch = 0; ch < 2; ++ch) {
                 uint32_t r[32], pk[16];
@@ -498,10 +498,8 @@ prefill_int8_kernel(const PrefillParams p) {
                     for (int e = 0; e < 4; ++e) {
                         const int c = 4 * c4 + e;
                         const float sv = small_int_to_float(r[c]) * kk[e];
-                        const bool seen = !kMasked || 32 * ch + c <= limit;
-                        if (seen) m_half = fmaxf(m_half, sv);
                         pr[e] = pf_ex2(fmaf(sv, row_factor, -m_use));
-                        if (!seen) pr[e] = 0.0f;
+                        if (kMasked && 32 * ch + c > limit) pr[e] = 0.0f;
                     }
                     l_try += pr[0] + pr[1];
                     l_try += pr[2] + pr[3];
@@ -513,11 +511,16 @@ prefill_int8_kernel(const PrefillParams p) {
                     *reinterpret_cast<uint4*>(prow + (8 * half + 4 * ch + kc) * 128) =
                         make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
             }
-            sm.xch[half][row] = m_half;
+            // The maximum is not tracked here: a row whose probabilities of this tile add up to more than 2^15
+            // has outgrown its reference (every probability is below 2^15 otherwise, harmless for P in T
+            // precision and for the fp32 sums), and so has a row that met its first visible key (its
+            // reference is still -inf and some probability is exp2(score), unbounded): redo those tiles.
+            sm.xch[half][row] = l_try - l_run;
             pair_sync(quarter);
-            const float m_tile = fmaxf(m_half, sm.xch[half ^ 1][row]) * row_factor;
-            // both warps that share these rows see the same maxima, hence take the same decision
-            if (__any_sync(0xffffffffu, m_tile > m_run + 8.0f)) return false;
+            const float tile_sum = (l_try - l_run) + sm.xch[half ^ 1][row];
+            // both warps that share these rows see the same sums, hence take the same decision
+            const bool outgrown = !(tile_sum <= 32768.0f) || (m_run == -INFINITY && tile_sum > 0.0f);
+            if (__any_sync(0xffffffffu, outgrown)) return false;
             l_run = l_try;
             return true;
         };
@@ -961,14 +964,14 @@ prefill_attn_kernel(const PrefillParams p) {
                 emit_chunk(r1, 1);
             }
         };
-        // After the first tile the reference maximum rarely moves, so the tile is first done in ONE pass
-        // against the current reference (scaled sums, their maximum and the probabilities together, nothing
-        // parked in TMEM, the raw sums left untouched); only when the maximum of some row of the warp does
-        // move is the tile redone by the two-pass code above.  Where the reference stays, both give the same bits.
+        // After the first tile the reference maximum rarely has to move, so the tile is first done in ONE
+        // pass against the current reference (scaled sums and probabilities together, nothing parked in TMEM,
+        // the raw sums left untouched); only when some row of the warp has outgrown its reference is the
+        // tile redone by the two-pass code above, which also finds the new maximum.
         auto softmax_one_pass = [&](auto masked_tag) -> bool {
             constexpr bool kMasked = decltype(masked_tag)::value;
             const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
-            float m_half = -INFINITY, l_try = l_run;
+            float l_try = l_run;
 #pragma unroll 1
             for (int ch = 0; ch < 2; ++ch) {
                 uint32_t r[32], pk[16];
@@ -982,10 +985,8 @@ prefill_attn_kernel(const PrefillParams p) {
                     for (int e = 0; e < 4; ++e) {
                         const int c = 4 * c4 + e;
                         const float sv = small_int_to_float(r[c]) * kk[e];
-                        const bool seen = !kMasked || 32 * ch + c <= limit;
-                        if (seen) m_half = fmaxf(m_half, sv);
                         pr[e] = pf_ex2(fmaf(sv, row_factor, -m_use));
-                        if (!seen) pr[e] = 0.0f;
+                        if (kMasked && 32 * ch + c > limit) pr[e] = 0.0f;
                     }
                     l_try += pr[0] + pr[1];
                     l_try += pr[2] + pr[3];
@@ -997,11 +998,16 @@ prefill_attn_kernel(const PrefillParams p) {
                     *reinterpret_cast<uint4*>(prow + (8 * half + 4 * ch + kc) * 128) =
                         make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
             }
-            sm.xch[half][row] = m_half;
+            // The maximum is not tracked here: a row whose probabilities of this tile add up to more than 2^15
+            // has outgrown its reference (every probability is below 2^15 otherwise, harmless for P in T
+            // precision and for the fp32 sums), and so has a row that met its first visible key (its
+            // reference is still -inf and some probability is exp2(score), unbounded): redo those tiles.
+            sm.xch[half][row] = l_try - l_run;
             pair_sync(quarter);
-            const float m_tile = fmaxf(m_half, sm.xch[half ^ 1][row]) * row_factor;
-            // both warps that share these rows see the same maxima, hence take the same decision
-            if (__any_sync(0xffffffffu, m_tile > m_run + 8.0f)) return false;
+            const float tile_sum = (l_try - l_run) + sm.xch[half ^ 1][row];
+            // both warps that share these rows see the same sums, hence take the same decision
+            const bool outgrown = !(tile_sum <= 32768.0f) || (m_run == -INFINITY && tile_sum > 0.0f);
+            if (__any_sync(0xffffffffu, outgrown)) return false;
             l_run = l_try;
             return true;
         };
