@@ -64,6 +64,9 @@ def parse_args():
                     choices=["decode_llama8b", "decode_qwen7b_planar", "decode_70b_long", "prefill_int8"])
     ap.add_argument("--batch", type=int, default=0,
                     help="override the workload's number of sequences (small cases for profiling)")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="profiling aid for head-sharded workloads on ONE GPU: time the shard rank 0 would hold "
+                         "at this world size (no exchange, no extras; the line says so in config.sharding)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--gather", default="both", choices=["both", "peer", "nccl"],
@@ -941,7 +944,12 @@ def run_gpu_arm(args, w: syn.Workload) -> None:
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    job = GpuJob(w, rank, world, device)
+    shard_of = args.shard_of if (world == 1 and args.shard_of > 1) else 0
+    job = GpuJob(w, rank, shard_of or world, device, sharding="by KV head" if shard_of else None)
+    if shard_of:
+        job.gather = None
+        job.out = job.out.clone()
+        args.no_extras = True
     sampler = ClockSampler(local) if rank == 0 else None
     m = measure_job(job, args, device, barrier, world, sampler)
 
@@ -957,7 +965,8 @@ def run_gpu_arm(args, w: syn.Workload) -> None:
             "ms_per_step": m["ms_per_step"], "timed_chunks_of_steps": m["chunks"], "higher_is_better": True,
             "scaling": "weak" if job.sharding == "by sequence" else "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(w, world, w.batch, job.sharding),
+            "config": workload_config(w, world, w.batch, job.sharding if not shard_of else
+                                      f"the shard of rank 0 of {shard_of} by KV head ({job.H} KV heads), no exchange"),
             "clocks": m["clocks"], "cuda_graph": m["graph"],
             "e2e": {"value": seqs_per_step / (m["e2e_ms_per_step"] * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"],

@@ -883,19 +883,25 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ seq_lens, int num
 // query head sits in slot (query head within its group of 8).  Lanes
 // gather the running maxima and row sums of up to 32 parts at a time; then the warp sums the
 // weighted partial outputs.  Which groups those are was recorded per sequence by the attention CTAs.
+// W = 1: a warp per row (the usual few parts per row).  W = 4: a CTA per row, warp s taking every fourth round
+// of 32 parts and the four partial sums combined through shared memory -- for long sequences on few heads,
+// where a row has dozens of parts and there are too few rows to hide the latency of walking them.
 constexpr int kMergeWarps = 4;
-template <typename T>
+template <typename T, int W>
 __global__ void __launch_bounds__(kMergeWarps * 32)
 decode_merge_kernel(const DecodeParams p) {
+    __shared__ float part_ml[W > 1 ? W : 1][2];
+    __shared__ float4 part_acc[W > 1 ? W : 1][32];
     const int lane = threadIdx.x & 31;
+    const int sub = (threadIdx.x >> 5) % W;
     // the lane's 4x4 block of R does not depend on the attention launch: fetch it before waiting for that
     float4 rr[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k)
         rr[k] = __ldg(reinterpret_cast<const float4*>(p.rotation + (4 * lane + k) * kHeadDim + 4 * lane));
     grid_dependency_wait();
-    const int64_t wq = static_cast<int64_t>(blockIdx.x) * kMergeWarps + (threadIdx.x >> 5);
-    if (wq >= static_cast<int64_t>(p.num_seqs) * p.Hq) return;
+    const int64_t wq = static_cast<int64_t>(blockIdx.x) * (kMergeWarps / W) + (threadIdx.x >> 5) / W;
+    if (wq >= static_cast<int64_t>(p.num_seqs) * p.Hq) return;          // (all warps of a row together)
     const int seq = static_cast<int>(wq / p.Hq), qh = static_cast<int>(wq % p.Hq);
     const int J = p.H * p.head_groups;
     const int kvh = qh / p.G, hl = qh % p.G;
@@ -922,7 +928,7 @@ decode_merge_kernel(const DecodeParams p) {
         const bool dense = total * J * min_w >=
                            weight_cum(static_cast<int64_t>(p.groups) * J, p.layer_ctas, p.num_layers, p.layer_w);
         float m_all = -INFINITY;
-        for (int g0 = g_first; g0 <= g_last; g0 += 32) {             // normally one round
+        for (int g0 = g_first + 32 * sub; g0 <= g_last; g0 += 32 * W) {             // normally one round
             const int gi = g0 + lane;
             const bool live = gi <= g_last &&
                               (dense || piece_begin(p, gi, total, J) < piece_begin(p, gi + 1, total, J));
@@ -942,7 +948,7 @@ decode_merge_kernel(const DecodeParams p) {
             l_all = l_all * rescale + l_round;
             m_all = m_new;
             const int n_here = min(32, g_last - g0 + 1);
-#pragma unroll 4
+#pragma unroll 8
             for (int k = 0; k < n_here; ++k) {
                 const float wk = __shfl_sync(0xffffffffu, w, k);
                 if (wk != 0.0f) {
@@ -950,6 +956,29 @@ decode_merge_kernel(const DecodeParams p) {
                         p.ws_o + ((((static_cast<int64_t>(g0 + k) + seq) * J + item) * slots + slot) << 7) + 4 * lane);
                     acc.x += wk * o.x; acc.y += wk * o.y; acc.z += wk * o.z; acc.w += wk * o.w;
                 }
+            }
+        }
+        if constexpr (W > 1) {                                   // combine the warps' partial sums in warp 0
+            if (lane == 0) { part_ml[sub][0] = m_all; part_ml[sub][1] = l_all; }
+            part_acc[sub][lane] = acc;
+        }
+    }
+    if constexpr (W > 1) {
+        __syncthreads();
+        if (sub != 0) return;
+        if (n > 0) {
+            float m = part_ml[0][0];
+#pragma unroll
+            for (int s2 = 1; s2 < W; ++s2) m = fmaxf(m, part_ml[s2][0]);
+            acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            l_all = 0.0f;
+#pragma unroll
+            for (int s2 = 0; s2 < W; ++s2) {
+                const float ms = part_ml[s2][0];
+                const float ws = ms == -INFINITY ? 0.0f : exp2f(ms - m);      // a warp without parts
+                const float4 a4 = part_acc[s2][lane];
+                acc.x += ws * a4.x; acc.y += ws * a4.y; acc.z += ws * a4.z; acc.w += ws * a4.w;
+                l_all += ws * part_ml[s2][1];
             }
         }
     }
@@ -1167,10 +1196,13 @@ static int launch_decode(DecodeParams& p, int nh, bool tma, cudaStream_t st) {
         if (e) return e;
     }
 
-    const long long warps = 1LL * p.num_seqs * p.Hq;
-    const unsigned grid = static_cast<unsigned>((warps + kMergeWarps - 1) / kMergeWarps);
+    // rows with many parts each (long sequences on few heads): a CTA per row instead of a warp per row
+    const long long rows = 1LL * p.num_seqs * p.Hq;
+    const bool wide = p.groups > 8LL * p.num_seqs;
+    const unsigned grid = static_cast<unsigned>(wide ? rows : (rows + kMergeWarps - 1) / kMergeWarps);
     if (decode_env().no_pdl) {
-        decode_merge_kernel<T><<<grid, kMergeWarps * 32, 0, st>>>(p);
+        if (wide) decode_merge_kernel<T, kMergeWarps><<<grid, kMergeWarps * 32, 0, st>>>(p);
+        else decode_merge_kernel<T, 1><<<grid, kMergeWarps * 32, 0, st>>>(p);
         return check_cuda(cudaGetLastError(), "rq_decode merge launch");
     }
     cudaLaunchConfig_t cfg{};
@@ -1183,7 +1215,8 @@ static int launch_decode(DecodeParams& p, int nh, bool tma, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&cfg, decode_merge_kernel<T>, p), "rq_decode merge launch");
+    return check_cuda(wide ? cudaLaunchKernelEx(&cfg, decode_merge_kernel<T, kMergeWarps>, p)
+                           : cudaLaunchKernelEx(&cfg, decode_merge_kernel<T, 1>, p), "rq_decode merge launch");
 }
 
 template <typename T>
