@@ -512,14 +512,22 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
             if constexpr (!v_by_tma) {
                 // V rows that do not start on 16-byte boundaries (1 or 2 KV heads on this GPU): the warp
                 // copies them with 4-byte cp.async, two rows per instruction, into the same swizzled order
+                // (instruction i copies rows 2i and 2i + 1; all addresses are bases plus multiples of i)
+                const int half = lane >> 4, word = lane & 15;
+                const int rows_left = seq_len - (tile * kUTile + 32 * warp + half);     // row 2i exists when 2i < rows_left
+                const int64_t two_slots = 2 * static_cast<int64_t>(p.total_bytes);
+                const uint8_t* const col = p.cache + lay.v_idx + kvh * kHalfDim + 4 * word;
+                const uint8_t* src0 = col + static_cast<int64_t>(s0 + half) * p.total_bytes;
+                const uint8_t* src1 = col + static_cast<int64_t>(s1 + half) * p.total_bytes;
+                const uint32_t dst = smem_u32(sm.stage[warp][1]) + half * kHalfDim + ((word & 3) << 2);
+                uint32_t chunk[4];                       // 16-byte chunk of this word under the row's swizzle, (row >> 1) & 3 == i & 3
+#pragma unroll
+                for (int c = 0; c < 4; ++c) chunk[c] = dst + ((((word >> 2) ^ c)) << 4);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const int row = 2 * i + (lane >> 4), word = lane & 15;
-                    if (tile * kUTile + 32 * warp + row < seq_len) {
-                        const int slot = (i < 8 ? s0 : s1) + (row & 15);
-                        cp_async4(smem_u32(sm.stage[warp][1] + row * kHalfDim + (((word >> 2) ^ ((row >> 1) & 3)) << 4) + ((word & 3) << 2)),
-                                  p.cache + static_cast<int64_t>(slot) * p.total_bytes + lay.v_idx + kvh * kHalfDim + 4 * word);
-                    }
+                    if (2 * i < rows_left) cp_async4(chunk[i & 3] + i * 2 * kHalfDim, i < 8 ? src0 : src1);
+                    if (i < 8) src0 += two_slots;
+                    else src1 += two_slots;
                 }
             }
         };
