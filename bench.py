@@ -628,6 +628,50 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     def e2e_tail():
         main.wait_event(read_back)            # the closing event covers the last read-back
 
+    # Jobs without an exchange get a leaner pipeline, because the form above is bound by the dozen stream
+    # operations Python issues per step: two graphs (one per landing buffer and output buffer) that begin
+    # with the copy of their landing buffer into the staging buffer, and ONE copy stream that, after step i,
+    # reads its output back and uploads the inputs of step i + 2 into the landing buffer step i has consumed.
+    # Seven stream operations per step; every step still has its own upload and its own read-back in the region.
+    if egraph is not None and job.gather is None and job.peer is None:
+        torch.cuda.synchronize(device)
+        outs = [job.out, torch.empty_like(job.out)]
+        pair = []
+        for b in range(2):
+            job.out = outs[b]
+
+            def step_b(b=b):
+                job.staging.copy_(landing[b], non_blocking=True)
+                job.step_with_table_update()
+
+            pair.append(capture(step_b, device, f"the end-to-end step ({b})"))
+        job.out = outs[0]
+        if all(g is not None for g in pair):
+            landed = [torch.cuda.Event() for _ in range(2)]
+            finished = [torch.cuda.Event() for _ in range(2)]
+            with torch.cuda.stream(uploader):
+                for b in range(2):
+                    landing[b].copy_(host_in, non_blocking=True)
+                    landed[b].record(uploader)
+            torch.cuda.synchronize(device)
+            turn[0] = 0
+
+            def e2e_step():                               # noqa: F811  (replaces the general form)
+                b = turn[0]
+                turn[0] ^= 1
+                main.wait_event(landed[b])
+                pair[b].replay()
+                finished[b].record(main)
+                uploader.wait_event(finished[b])
+                with torch.cuda.stream(uploader):
+                    host_out.copy_(outs[b], non_blocking=True)
+                    landing[b].copy_(host_in, non_blocking=True)
+                    landed[b].record(uploader)
+
+            def e2e_tail():                               # noqa: F811
+                main.wait_event(landed[0])
+                main.wait_event(landed[1])
+
     for _ in range(4):
         e2e_step()
     barrier()
@@ -635,6 +679,8 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     barrier()
     e2e_tail()
     torch.cuda.synchronize(device)
+    # what reached the host is what the device holds (outside the timed region)
+    read_back_ok = bool(torch.equal(host_out, result.cpu()))
 
     t = torch.tensor([ms_chunk, e2e_ms, decode_eager_ms, decode_graph_ms or decode_eager_ms, compress_ms,
                       nogather_ms or 0.0, e2e_serial_ms], dtype=torch.float64, device=device)
@@ -646,7 +692,8 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
             "decode_kernel_ms": decode_kernel_ms, "decode_kernel_ms_eager": decode_eager_ms,
             "decode_in_graph": dgraph is not None, "compress_ms": compress_ms,
             "nogather_ms": nogather_ms if nogather_ms > 0 else None, "clocks": clocks,
-            "graph": graph is not None, "h2d": host_in.numel(), "d2h": host_out.numel() * host_out.element_size()}
+            "graph": graph is not None, "h2d": host_in.numel(), "d2h": host_out.numel() * host_out.element_size(),
+            "read_back_ok": read_back_ok}
 
 
 # --------------------------------------------------------------------------------------------
@@ -971,10 +1018,11 @@ def run_gpu_arm(args, w: syn.Workload) -> None:
             "e2e": {"value": seqs_per_step / (m["e2e_ms_per_step"] * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"],
                     "serial_value": seqs_per_step / (m["e2e_serial_ms_per_step"] * 1e-3),
+                    "read_back_equals_device_output": m["read_back_ok"],
                     "how": "per step: one pinned staging buffer -> one H2D copy, graph replay (block-table delta + "
-                           "compress + decode), one D2H copy of the output; three-stage pipeline over steps (upload "
-                           "stream, compute stream, read-back stream, two landing buffers), so a step's copies "
-                           "overlap its neighbours' compute; serial_value is the same without overlap (one stream)"},
+                           "compress + decode), one D2H copy of the output; pipelined over steps (copy stream and "
+                           "compute stream, two landing buffers and two output buffers), so a step's copies overlap "
+                           "its neighbours' compute; serial_value is the same without overlap (one stream)"},
             "gpu_launches": job.launches_per_step * args.steps * m["chunks"],
             "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel (+ merge kernel)",
                          "achieved": achieved, "peak": peak["hbm_gbs"], "peak_kind": f"{peak['kind']} copy bandwidth",
