@@ -598,7 +598,7 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     # memory and every step's output still reaches the host inside the timed region.
     main = torch.cuda.current_stream(device)
     uploader, reader = torch.cuda.Stream(device), torch.cuda.Stream(device)
-    landing = [torch.empty_like(job.staging) for _ in range(2)]
+    landing = [job.staging.clone() for _ in range(2)]
     uploaded = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
     computed, read_back = torch.cuda.Event(), torch.cuda.Event()
@@ -634,6 +634,9 @@ def measure_job(job: GpuJob, args, device, barrier, world: int, sampler=None) ->
     # reads its output back and uploads the inputs of step i + 2 into the landing buffer step i has consumed.
     # Seven stream operations per step; every step still has its own upload and its own read-back in the region.
     if egraph is not None and job.gather is None and job.peer is None:
+        # the landing buffers hold real inputs before anything replays a graph that reads them
+        for b in range(2):
+            landing[b].copy_(host_in, non_blocking=True)
         torch.cuda.synchronize(device)
         outs = [job.out, torch.empty_like(job.out)]
         pair = []
