@@ -84,20 +84,25 @@ __device__ __forceinline__ void load8(const T* src, float* x) {
     }
 }
 
-// What a thread keeps for the whole launch: the two 4x4 rotation blocks of its elements
-// (thread j of a row owns blocks 2j and 2j+1), as rot[half][out jj][in k].
+// What a thread needs of R for the whole launch: the two 4x4 blocks of its elements (thread j of a row owns
+// blocks 2j and 2j + 1), as [half][out jj][in k].  The CTA keeps them in shared memory, 36 floats apart per
+// thread slot so that the 16-byte chunks of eight consecutive threads fall into different banks (the two rows
+// of a warp read the same addresses); keeping them in 32 registers per thread instead costs the fourth CTA per SM.
+constexpr int kRotPitch = 36;
 struct ThreadRotation {
-    float r[32];
+    const float* s;
 };
 __device__ __forceinline__ ThreadRotation load_rotation(const float* __restrict__ rotation, int j) {
-    ThreadRotation t;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const int g = 2 * j + (i >> 4), jj = (i >> 2) & 3, k = i & 3;
-        t.r[i] = __ldg(rotation + (4 * g + jj) * kHeadDim + 4 * g + k);          // R[4g+jj][4g+k]
+    __shared__ __align__(16) float rot_s[16 * kRotPitch];
+    for (int i = threadIdx.x; i < 512; i += kCompressThreads) {
+        const int t = i >> 5, e = i & 31;
+        const int g = 2 * t + (e >> 4), jj = (e >> 2) & 3, k = e & 3;
+        rot_s[t * kRotPitch + e] = __ldg(rotation + (4 * g + jj) * kHeadDim + 4 * g + k);
     }
-    return t;
+    __syncthreads();
+    return ThreadRotation{rot_s + j * kRotPitch};
 }
+
 
 // Number of boundaries strictly below v.  The boundaries ascend, so "bd[b] < v" is true for a
 // prefix of them and a binary search over that prefix gives the count with log2(NB + 1) compares
@@ -164,7 +169,8 @@ __device__ __forceinline__ uint32_t compress_chunk(const float (&x)[8], int j, f
         uint32_t idx[4];
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-            const float* r = &rot.r[16 * half + 4 * jj];
+            const float4 r4 = *reinterpret_cast<const float4*>(rot.s + 16 * half + 4 * jj);
+            const float r[4] = {r4.x, r4.y, r4.z, r4.w};
             float acc = __fmul_rn(x0, r[0]);
             acc = __fmaf_rn(x1, r[1], acc);
             acc = __fmaf_rn(x2, r[2], acc);
@@ -241,7 +247,7 @@ __device__ __forceinline__ void store_rows(const CompressParams& p, int kv, cons
     }
 }
 template <typename T>
-__global__ void __launch_bounds__(kCompressThreads, 2)
+__global__ void __launch_bounds__(kCompressThreads, 4)
 compress_store_kernel(const CompressParams p) {
     __shared__ __align__(16) float sq[kRowsPerCta][16 * 8];
     const int j = threadIdx.x & 15;
