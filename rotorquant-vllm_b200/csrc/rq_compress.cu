@@ -14,11 +14,11 @@
 //   rotate : out_j = fma(x3,R[j][3], fma(x2,R[j][2], fma(x1,R[j][1], x0*R[j][0]))) per 4x4 block
 //   bucket : number of boundaries strictly below the value
 //
-// Mapping.  Sixteen threads share a row of 128 values: thread j owns elements 8j..8j+7 (one
-// 16-byte load for 2-byte inputs), i.e. two rotation blocks and one 32-bit word of packed
-// output, so loads and stores of a half-warp are contiguous.  Only the norm needs the whole
-// row: the squares go through shared memory, threads 0..7 of the row form the eight running
-// sums in the prescribed order, and the left-to-right combination is done with shuffles.
+// Mapping.  The cache-write path (compress + store) gives a row of 128 values to four threads, 32
+// elements, eight rotation blocks and one 16-byte store each; the plain rows-to-rows path gives it to
+// sixteen threads of 8 elements.  Only the norm needs the whole row: the squares go through shared
+// memory, a few threads of the row form the eight running sums in the prescribed order, and the
+// left-to-right combination is done with shuffles.
 #include "rq_common.cuh"
 
 namespace rq {
@@ -27,6 +27,7 @@ constexpr int kCompressThreads = 256;                 // 16 rows per CTA
 constexpr int kRowsPerCta = kCompressThreads / 16;
 constexpr int kCompressGrid = 148 * 4;                // the grid walks the rows: at most 4 CTAs per SM
 constexpr int kRowBatch = 2;                          // rows fetched ahead per 16-thread group and step
+constexpr int64_t kWideFromRows = 16384;              // launches with this many rows per kind use four threads per row
 
 struct CompressParams {
     const void* src[2];          // key, value (or x, unused)
@@ -184,10 +185,14 @@ __device__ __forceinline__ uint32_t compress_chunk(const float (&x)[8], int j, f
     return word;
 }
 
-// Store variant.  A fixed grid walks the rows: first all K rows (token-major, head-minor), then
-// all V rows, two rows per warp at a time, the elements of a step's rows all requested before the
-// first is processed.  Every row's 16 threads write its 64 index bytes and its norm straight into the
-// token's cache slot; the K row of head 0 also zeroes the slot's padding.
+// ---- store variant for small launches: sixteen threads per row -------------------------------------
+//
+// The decode step compresses one token per sequence: a few hundred rows.  With 8 elements per thread the
+// dependency chain of a row is a quarter as long as with 32, and the rows spread over four times as many
+// threads, which is what counts when the launch cannot fill the GPU anyway.  A fixed grid walks first all K
+// rows (token-major, head-minor), then all V rows, two rows per warp at a time, the elements of a step's
+// rows all requested before the first is processed.  Every row's 16 threads write its 64 index bytes and its
+// norm straight into the token's cache slot; the K row of head 0 also zeroes the slot's padding.
 template <typename T, int NB>
 __device__ __forceinline__ void store_rows(const CompressParams& p, int kv, const ThreadRotation& rot,
                                            float* sq_row, int j) {
@@ -257,6 +262,144 @@ compress_store_kernel(const CompressParams p) {
     for (int kv = 0; kv < 2; ++kv) {
         if (p.n_bounds[kv] <= 7) store_rows<T, 7>(p, kv, rot, sq_row, j);
         else store_rows<T, 15>(p, kv, rot, sq_row, j);
+    }
+}
+
+// ---- store variant for large launches: four threads per row -----------------------------------------
+//
+// A fixed grid (two CTAs per SM) walks the rows: first all K rows (token-major, head-minor), then all V rows.
+// Every row's threads write its 64 index bytes and its norm straight into the token's cache slot; the K row of
+// head 0 also zeroes the slot's padding.  The arithmetic is that of compress_chunk with 32 elements per thread: thread t of a row owns elements 32t .. 32t + 31 (four
+// 16-byte loads for 2-byte inputs, eight rotation blocks, one 16-byte store of packed indices), a warp works
+// on eight rows at a time.  The per-row and per-thread overhead (addressing, slot lookup, the exchange for the
+// in-order sums, the square root, stores) is spread over four times as many elements as with 16 threads per row.
+// In-order sums: the squares go to shared memory as [c][l] (element 8c + l); thread t forms the running sums
+// of lanes l = 2t and 2t + 1 over c = 0..15, and every thread then adds the eight lane sums left to right.
+constexpr int kWideThreads = 256;
+constexpr int kWideRowsPerWarp = 8;
+constexpr int kWideRowsPerCta = (kWideThreads / 32) * kWideRowsPerWarp;   // 64
+constexpr int kWideSqPitch = 136;            // floats per row of squares: 128 + 8, spreads rows over the banks
+constexpr int kWideRotPitch = 132;           // floats per thread slot of rotation blocks: 8 x 16 + 4
+constexpr int kWideGrid = 148 * 2;           // the grid walks the rows: two CTAs per SM
+
+template <typename T, int NB>
+__device__ __forceinline__ void store_rows_wide(const CompressParams& p, int kv, const float* rot_t, float* sq_row,
+                                                int t) {
+    float bd[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) bd[b] = __ldg(p.bounds[kv] + b);
+    const int H = p.H;
+    const SlotLayout lay = slot_layout(H);
+    const uint32_t rows = static_cast<uint32_t>(p.num_tokens) * static_cast<uint32_t>(H);
+    const uint32_t step = gridDim.x * kWideRowsPerCta;
+    const int lane = threadIdx.x & 31;
+    const uint32_t first = blockIdx.x * kWideRowsPerCta + (threadIdx.x >> 5) * kWideRowsPerWarp + (lane >> 2);
+    const uint32_t warp_first = first - (lane >> 2);
+    const T* src = static_cast<const T*>(p.src[kv]);
+
+    // the eight rows of a warp run in lock step (__syncwarp around the exchange): loop on the warp's first row
+    for (uint32_t wr = warp_first, r = first; wr < rows; wr += step, r += step) {
+        const uint32_t rr = r < rows ? r : 0u;                      // rows past the end compute on row 0, store nothing
+        uint32_t token, h;
+        if (p.h_shift >= 0) { token = rr >> p.h_shift; h = rr & (H - 1); }
+        else { token = rr / H; h = rr - token * H; }
+        const T* row_src = src + token * p.token_stride[kv] + static_cast<int64_t>(h) * p.head_stride[kv] + 32 * t;
+        const int64_t slot = __ldg(p.slot_mapping + token);
+        float x[32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) load8<T>(row_src + 8 * c, x + 8 * c);
+
+        // squares, published for the in-order lane sums: sq_row[8 c + l], this thread's c = 4t .. 4t + 3
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float* dst = sq_row + 8 * (4 * t + c);
+            *reinterpret_cast<float4*>(dst) = make_float4(__fmul_rn(x[8 * c], x[8 * c]), __fmul_rn(x[8 * c + 1], x[8 * c + 1]),
+                                                         __fmul_rn(x[8 * c + 2], x[8 * c + 2]), __fmul_rn(x[8 * c + 3], x[8 * c + 3]));
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(__fmul_rn(x[8 * c + 4], x[8 * c + 4]), __fmul_rn(x[8 * c + 5], x[8 * c + 5]),
+                                                             __fmul_rn(x[8 * c + 6], x[8 * c + 6]), __fmul_rn(x[8 * c + 7], x[8 * c + 7]));
+        }
+        __syncwarp();
+        float s_even, s_odd;                                        // running sums of lanes 2t and 2t + 1
+        {
+            const float2 v0 = *reinterpret_cast<const float2*>(sq_row + 2 * t);
+            s_even = v0.x; s_odd = v0.y;
+#pragma unroll
+            for (int c = 1; c < 16; ++c) {
+                const float2 v = *reinterpret_cast<const float2*>(sq_row + 8 * c + 2 * t);
+                s_even = __fadd_rn(s_even, v.x);
+                s_odd = __fadd_rn(s_odd, v.y);
+            }
+        }
+        const int row_lane0 = lane & ~3;
+        float tot = __shfl_sync(0xffffffffu, s_even, row_lane0);
+        tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, s_odd, row_lane0));
+#pragma unroll
+        for (int u = 1; u < 4; ++u) {
+            tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, s_even, row_lane0 + u));
+            tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, s_odd, row_lane0 + u));
+        }
+        __syncwarp();                                               // sq_row may be rewritten by the next row
+        const float norm = __fsqrt_rn(tot);
+        const float denom = __fadd_rn(norm, 1e-10f);
+
+        uint32_t words[4];
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {                               // rotation block 8t + b = elements 4b .. 4b + 3 of x
+            const float x0 = __fdiv_rn(x[4 * b], denom), x1 = __fdiv_rn(x[4 * b + 1], denom);
+            const float x2 = __fdiv_rn(x[4 * b + 2], denom), x3 = __fdiv_rn(x[4 * b + 3], denom);
+            uint32_t idx[4];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const float4 r4 = *reinterpret_cast<const float4*>(rot_t + 16 * b + 4 * jj);
+                float acc = __fmul_rn(x0, r4.x);
+                acc = __fmaf_rn(x1, r4.y, acc);
+                acc = __fmaf_rn(x2, r4.z, acc);
+                acc = __fmaf_rn(x3, r4.w, acc);
+                idx[jj] = count_below<NB>(bd, acc);
+            }
+            const uint32_t b0 = (idx[0] << 4) | idx[1];
+            const uint32_t b1 = (idx[2] << 4) | idx[3];
+            const uint32_t half16 = b0 | (b1 << 8);
+            if (b & 1) words[b >> 1] |= half16 << 16;
+            else words[b >> 1] = half16;
+        }
+        if (r < rows && slot >= 0 && slot < p.num_slots) {
+            uint8_t* dst = p.cache + slot * p.total_bytes;
+            uint8_t* idx_dst = dst + (kv ? lay.v_idx : lay.k_idx) + h * kHalfDim + 16 * t;
+            if ((reinterpret_cast<uintptr_t>(idx_dst) & 15u) == 0) {
+                *reinterpret_cast<uint4*>(idx_dst) = make_uint4(words[0], words[1], words[2], words[3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(idx_dst)[i] = words[i];
+            }
+            if (t == 0) *reinterpret_cast<float*>(dst + (kv ? lay.v_norm : lay.k_norm) + 4 * h) = norm;
+            if (p.write_padding && kv == 0 && h == 0) {
+                const int units = (lay.total - lay.payload_end) / 8;
+                for (int u = t; u < units; u += 4)
+                    *reinterpret_cast<uint2*>(dst + lay.payload_end + 8 * u) = make_uint2(0u, 0u);
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWideThreads, 2)
+compress_store_wide_kernel(const CompressParams p) {
+    __shared__ __align__(16) float sq[kWideRowsPerCta * kWideSqPitch];
+    __shared__ __align__(16) float rot_s[4 * kWideRotPitch];
+    // rot_s[t][b][jj][k] = R[4g + jj][4g + k], g = 8t + b
+    for (int i = threadIdx.x; i < 512; i += kWideThreads) {
+        const int g = i >> 4, jj = (i >> 2) & 3, k = i & 3;
+        rot_s[(g >> 3) * kWideRotPitch + (g & 7) * 16 + 4 * jj + k] = __ldg(p.rotation + (4 * g + jj) * kHeadDim + 4 * g + k);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, t = lane & 3;
+    float* sq_row = sq + ((threadIdx.x >> 5) * kWideRowsPerWarp + (lane >> 2)) * kWideSqPitch;
+    const float* rot_t = rot_s + t * kWideRotPitch;
+#pragma unroll 1
+    for (int kv = 0; kv < 2; ++kv) {
+        if (p.n_bounds[kv] <= 7) store_rows_wide<T, 7>(p, kv, rot_t, sq_row, t);
+        else store_rows_wide<T, 15>(p, kv, rot_t, sq_row, t);
     }
 }
 
@@ -410,6 +553,12 @@ static int check_bounds_count(int n, const char* what) {
 template <typename T>
 static void launch_store(const CompressParams& p, cudaStream_t st) {
     const int64_t rows = p.num_tokens * p.H;                               // per kind
+    if (rows >= kWideFromRows) {
+        const int64_t want = (rows + kWideRowsPerCta - 1) / kWideRowsPerCta;
+        const unsigned grid = static_cast<unsigned>(want < kWideGrid ? want : kWideGrid);
+        compress_store_wide_kernel<T><<<grid, kWideThreads, 0, st>>>(p);
+        return;
+    }
     const int64_t want = (rows + kRowsPerCta - 1) / kRowsPerCta;
     const unsigned grid = static_cast<unsigned>(want < kCompressGrid ? want : kCompressGrid);
     compress_store_kernel<T><<<grid, kCompressThreads, 0, st>>>(p);
