@@ -342,11 +342,34 @@ __device__ __forceinline__ void store_rows_wide(const CompressParams& p, int kv,
         const float norm = __fsqrt_rn(tot);
         const float denom = __fadd_rn(norm, 1e-10f);
 
+        // The 32 IEEE divisions x / denom, through double precision: (float)((double)x * (1.0 / (double)denom)) is
+        // the correctly rounded fp32 quotient whenever that quotient is a normal number -- a quotient of two
+        // 24-bit significands stays at least 2^-49 (relative) away from every midpoint between adjacent floats,
+        // and the double-precision value is within 2^-52 of the exact quotient, so both round the same way;
+        // zeros, infinities and NaNs come out as the division gives them.  Quotients in or next to the subnormal
+        // range (coarser grid, exact ties possible) take the division instruction itself.  One reciprocal per
+        // row and no branch per element: the quotients are independent instruction streams, not 32 basic blocks.
+        {
+            const double rcp = __ddiv_rn(1.0, static_cast<double>(denom));
+            float q[32];
+            bool tiny = false;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const double pr = __dmul_rn(static_cast<double>(x[i]), rcp);
+                q[i] = __double2float_rn(pr);
+                tiny |= fabs(pr) < 0x1p-125 && pr != 0.0;
+            }
+            if (tiny) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) q[i] = __fdiv_rn(x[i], denom);
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = q[i];
+        }
         uint32_t words[4];
 #pragma unroll
         for (int b = 0; b < 8; ++b) {                               // rotation block 8t + b = elements 4b .. 4b + 3 of x
-            const float x0 = __fdiv_rn(x[4 * b], denom), x1 = __fdiv_rn(x[4 * b + 1], denom);
-            const float x2 = __fdiv_rn(x[4 * b + 2], denom), x3 = __fdiv_rn(x[4 * b + 3], denom);
+            const float x0 = x[4 * b], x1 = x[4 * b + 1], x2 = x[4 * b + 2], x3 = x[4 * b + 3];
             uint32_t idx[4];
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {

@@ -171,3 +171,42 @@ def test_full_size_prefill_compress_properties():
     rows = rq_exact.build_slots(key[sample].float().cpu().numpy(), value[sample].float().cpu().numpy(),
                                 p["R"].numpy(), p["k_boundaries"].numpy(), p["v_boundaries"].numpy())
     assert np.array_equal(f1[slots[sample]].cpu().numpy(), rows)
+
+
+def test_large_launch_divisions_equal_the_ieee_quotients_on_extreme_rows():
+    """The large-launch mapping forms x / (norm + 1e-10) through double precision where the quotient is a
+    normal number and with the division instruction next to the subnormal range.  Rows built to hit both
+    sides: one huge element beside tiny ones (quotients of 1e-38 .. 1e-45 and exact zeros), whole rows of
+    tiny or huge magnitude, all-zero rows (denominator 1e-10), and ordinary rows; every byte and norm must equal
+    the exact-arithmetic oracle on a sample, and the small-launch kernel (other mapping, plain divisions)
+    must give the same bytes for the same tokens."""
+    p = gpu_util.params("iso_fast", 3, 3)
+    gen = torch.Generator(device=DEV).manual_seed(7)
+    N, H = 4096, 8                                    # 32768 rows per kind: the large-launch mapping
+    key = torch.randn(N, H, 128, generator=gen, device=DEV)
+    value = torch.randn(N, H, 128, generator=gen, device=DEV)
+    key[0::8] *= 1e-30
+    key[0::8, :, 5] = 3e8                             # quotients around 1e-38: the subnormal border
+    key[1::8] *= 1e-37
+    key[1::8, :, 9] = 2.5                             # quotients around 1e-37 .. 1e-45
+    key[2::8] *= 1e-35                                # tiny rows, ordinary quotients
+    key[3::8] *= 1e30                                 # huge rows
+    key[4::8] = 0.0                                   # norm 0: denominator 1e-10
+    value[0::8, :, 100] = 1e38
+    value[1::8] *= 1e-38
+    key, value = key.to(torch.bfloat16), value.to(torch.bfloat16)
+    slots = torch.randperm(N, device=DEV)
+    args = (p["R"].to(DEV), p["k_boundaries"].to(DEV), p["v_boundaries"].to(DEV))
+    big = torch.zeros(N // 16, 16, 2048, dtype=torch.uint8, device=DEV)
+    _cuda().compress_and_store(key, value, big, slots, *args)
+    flat = big.reshape(N, 2048)
+    sample = torch.arange(0, N, 61, device=DEV)
+    sample = torch.unique(torch.cat([sample, torch.arange(0, 64, device=DEV)]))
+    rows = rq_exact.build_slots(key[sample].float().cpu().numpy(), value[sample].float().cpu().numpy(),
+                                p["R"].numpy(), p["k_boundaries"].numpy(), p["v_boundaries"].numpy())
+    assert np.array_equal(flat[slots[sample]].cpu().numpy(), rows)
+    # the same tokens in launches of 256 tokens (2048 rows per kind: the small-launch mapping)
+    small = torch.zeros_like(big)
+    for lo in range(0, N, 256):
+        _cuda().compress_and_store(key[lo:lo + 256], value[lo:lo + 256], small, slots[lo:lo + 256], *args)
+    assert torch.equal(big, small)
