@@ -355,9 +355,8 @@ __device__ __forceinline__ void store_rows_wide(const CompressParams& p, int kv,
             bool tiny = false;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                const double pr = __dmul_rn(static_cast<double>(x[i]), rcp);
-                q[i] = __double2float_rn(pr);
-                tiny |= fabs(pr) < 0x1p-125 && pr != 0.0;
+                q[i] = __double2float_rn(__dmul_rn(static_cast<double>(x[i]), rcp));
+                tiny |= fabsf(q[i]) < 0x1p-124f && x[i] != 0.0f;        // (a zero quotient of a nonzero element too)
             }
             if (tiny) {
 #pragma unroll
